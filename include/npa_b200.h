@@ -1,0 +1,250 @@
+/*
+ * npa_b200 -- C ABI of the B200 (sm_100a) SPH neighbour-perception library.
+ *
+ * Every entry point replaces one method of the reference's native module
+ * `sph_cuda` (sphops/sph_cuda.cu, bound with nanobind at sph_cuda.cu:3229-3441)
+ * and is what a ctypes / nanobind / pybind11 stub on the reference side binds.
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers unless the name says "host".  Float
+ *    tensors are contiguous fp32, index tensors contiguous int32.
+ *  - Positions are [B, N, P] with P = 2 (dim 2) or P = 4 (dim 3, w ignored on
+ *    input and written as 0 on output), as in the reference
+ *    (sphops/utils.cuh:14-111, sph_cuda.cu:1898).
+ *  - Inputs are const, outputs and scratch are caller-allocated; the library
+ *    allocates nothing, never synchronises and keeps no state between calls
+ *    except the thread-local text returned by npa_last_error().
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - Return value: NPA_OK (0) or a negative npa_status; on error nothing has
+ *    been launched.  No C++ exception crosses this boundary.
+ *  - `mass` may be NULL: every particle then has mass 1.0
+ *    (sphops/sph.py:11-14, sph_cuda.cu:1843).
+ */
+#ifndef NPA_B200_H
+#define NPA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NPA_B200_ABI_VERSION 1
+
+typedef enum npa_status {
+    NPA_OK = 0,
+    NPA_ERR_INVALID_ARGUMENT = -1, /* bad geometry, NULL pointer, size mismatch  */
+    NPA_ERR_UNSUPPORTED = -2,      /* e.g. Morton hash on a non power-of-two grid */
+    NPA_ERR_CUDA = -3,             /* a CUDA runtime call / launch failed         */
+    NPA_ERR_SCRATCH_TOO_SMALL = -4 /* scratch_bytes < npa_grid_scratch_bytes()    */
+} npa_status;
+
+/* Boundary condition, sphops/utils.cuh:282-286. */
+enum { NPA_BOUNDARY_CLAMPED = 0, NPA_BOUNDARY_PERIODIC = 1 };
+/* Cell hash order: linear ("grid" mode) or Morton ("particle" mode),
+ * sphops/utils.cuh:442-453. */
+enum { NPA_HASH_LINEAR = 0, NPA_HASH_MORTON = 1 };
+
+/*
+ * Geometry of one HashGrid; replaces the constructor arguments of the eight
+ * `{,V}HashGrid{2D,3D}{Periodic,Box}` classes (sph_cuda.cu:3049-3093, ctor
+ * `(gx, gy[, gz], eps, particle_count, batch_size, max_particles_per_block)`).
+ * Plain data, passed by pointer and copied; the library keeps no reference.
+ */
+typedef struct npa_grid {
+    int32_t dim;        /* 2 or 3                                            */
+    int32_t boundary;   /* NPA_BOUNDARY_*                                    */
+    int32_t hash;       /* NPA_HASH_*                                        */
+    int32_t grid[3];    /* cells per axis (grid[2] ignored when dim == 2)    */
+    double eps;         /* cell size == cut-off radius h                     */
+    int32_t batch;      /* B, independent particle systems                   */
+    int32_t particles;  /* N, particles per system                           */
+    int32_t max_particles_per_block; /* MPB: a work item covers <= MPB particles of one cell */
+} npa_grid;
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *npa_last_error(void);
+/* NPA_B200_ABI_VERSION the library was built with. */
+int npa_abi_version(void);
+
+/* Cells per system (product of grid[0..dim)), or a negative npa_status. */
+int64_t npa_grid_num_cells(const npa_grid *g);
+/* Rows of `block_info`: B * min(N, cells + ceil(N / MPB))
+ * (sph_cuda.cu:1851-1853).  Unlike the reference, the same size is used with
+ * the Morton hash, because the work list drives every kernel here. */
+int64_t npa_grid_max_blocks(const npa_grid *g);
+/* Bytes of device scratch npa_grid_build() needs (cell histogram, cursors,
+ * cell ids, unsorted slots, scan partials); replaces the cudaMalloc'ed members
+ * of the reference's HashGrid (sph_cuda.cu:1881-1895). */
+int64_t npa_grid_scratch_bytes(const npa_grid *g);
+
+/*
+ * Uniform-grid binning; replaces HashGrid::initialize (sph_cuda.cu:1926-1992:
+ * grid_count_particles, two CUB scans, grid_compute_permutation,
+ * assign_block_info).
+ *   x            [B, N, P]            in
+ *   permutation  [B, N]               out: destination slot of particle i inside its system
+ *   bin_offsets  [B*cells + 1]        out: exclusive scan of the cell counts over all systems
+ *                                          (entry b*cells + c includes b*N; last entry = B*N)
+ *   block_info   [max_blocks, 4]      out: (global cell, offset in cell, particle count, system)
+ *                                          per work item, in cell order; unused tail rows are zero
+ *   scratch      scratch_bytes        scratch, contents undefined on entry and exit
+ * The slot order inside a cell is the original particle order (a stable
+ * counting sort), so the result is deterministic; the reference's order inside
+ * a cell depends on atomic arrival order (sph_cuda.cu:81-83).
+ */
+int npa_grid_build(const npa_grid *g, const float *x, int32_t *permutation,
+                   int32_t *bin_offsets, int32_t *block_info, void *scratch,
+                   int64_t scratch_bytes, void *stream);
+
+/*
+ * Reorder into cell order: out[perm[i]] = in[i].  Replaces
+ * HashGrid::bin_particles (sph_cuda.cu:1994-2024, kernel apply_permutation
+ * :86-123).  Any of the (in, out) pairs may be NULL together to skip it.
+ *   x/x_out [B,N,P]   s/s_out [B,N,C]   mass/mass_out [B,N]
+ */
+int npa_bin_particles(const npa_grid *g, int32_t channels, const float *x,
+                      const float *s, const float *mass,
+                      const int32_t *permutation, float *x_out, float *s_out,
+                      float *mass_out, void *stream);
+
+/*
+ * Inverse reorder: out[i] = in[perm[i]].  Replaces
+ * HashGrid::backward_bin_particles (sph_cuda.cu:2026-2056, kernel
+ * backward_apply_permutation :125-167); also what unbin_particles calls
+ * (sphops/sph.py:187-198).
+ */
+int npa_unbin_particles(const npa_grid *g, int32_t channels, const float *x_bin,
+                        const float *s_bin, const float *mass_bin,
+                        const int32_t *permutation, float *x_out, float *s_out,
+                        float *mass_out, void *stream);
+
+/* ---- single-operator forward passes (inputs are in cell order) ---------- */
+
+/* count[B,N] = number of j with |x_j - x_i|^2 < h^2, self included.
+ * Replaces HashGrid::count_forward (sph_cuda.cu:2127-2189). */
+int npa_count_forward(const npa_grid *g, const float *x_bin, float *count,
+                      const int32_t *bin_offsets, const int32_t *block_info,
+                      void *stream);
+
+/* rho[B,N] = c_s * sum_j m_j (h^2 - r^2)^3.
+ * Replaces HashGrid::density_forward (sph_cuda.cu:2058-2125). */
+int npa_density_forward(const npa_grid *g, const float *x_bin, const float *mass,
+                        float *rho, const int32_t *bin_offsets,
+                        const int32_t *block_info, void *stream);
+
+/* out[B,N,C] = c_s * sum_j s_j (m_j / rho_j) (h^2 - r^2)^3.
+ * Replaces HashGrid::blur_forward (sph_cuda.cu:2191-2277). */
+int npa_blur_forward(const npa_grid *g, int32_t channels, const float *x_bin,
+                     const float *rho, const float *mass, const float *s_bin,
+                     float *s_blur, const int32_t *bin_offsets,
+                     const int32_t *block_info, void *stream);
+
+/* out[B,N,C,D] = c_g * sum_j (s_j - s_i) (m_j / rho_j) 3(h-r)^2/r (x_j - x_i).
+ * Replaces HashGrid::gradient_forward (sph_cuda.cu:2279-2365). */
+int npa_gradient_forward(const npa_grid *g, int32_t channels, const float *x_bin,
+                         const float *rho, const float *mass, const float *s_bin,
+                         float *s_grad, const int32_t *bin_offsets,
+                         const int32_t *block_info, void *stream);
+
+/* out[B,N,D] = c_g * sum_j m_j 3(h-r)^2/r (x_j - x_i).
+ * Replaces HashGrid::density_gradient_forward (sph_cuda.cu:2367-2431). */
+int npa_density_gradient_forward(const npa_grid *g, const float *x_bin,
+                                 const float *mass, float *rho_grad,
+                                 const int32_t *bin_offsets,
+                                 const int32_t *block_info, void *stream);
+
+/* out[B,N,D,D] = c_g * sum_j (m_j / rho_j) 3(h-r)^2/r (x_j-x_i)(x_j-x_i)^T.
+ * Replaces HashGrid::moment_matrix_forward (sph_cuda.cu:2433-2499). */
+int npa_moment_matrix_forward(const npa_grid *g, const float *x_bin,
+                              const float *rho, const float *mass, float *moment,
+                              const int32_t *bin_offsets,
+                              const int32_t *block_info, void *stream);
+
+/* ---- single-operator backward passes ------------------------------------ *
+ * Each `grad_*` output may be NULL: that gradient is then not computed (the
+ * reference's dLdx / dLds / dLdrho flags, sph_cuda.cu:2624,2854).           */
+
+/* Replaces HashGrid::density_backward (sph_cuda.cu:2501-2578). */
+int npa_density_backward(const npa_grid *g, const float *x_bin, const float *mass,
+                         const float *dL_drho, float *grad_x,
+                         const int32_t *bin_offsets, const int32_t *block_info,
+                         void *stream);
+
+/* Replaces HashGrid::blur_backward (sph_cuda.cu:2580-2728). */
+int npa_blur_backward(const npa_grid *g, int32_t channels, const float *x_bin,
+                      const float *rho, const float *mass, const float *s_bin,
+                      const float *dL_dblur, float *grad_x, float *grad_s,
+                      float *grad_rho, const int32_t *bin_offsets,
+                      const int32_t *block_info, void *stream);
+
+/* Replaces HashGrid::gradient_backward (sph_cuda.cu:2810-2958). */
+int npa_gradient_backward(const npa_grid *g, int32_t channels, const float *x_bin,
+                          const float *rho, const float *mass, const float *s_bin,
+                          const float *dL_dgrad, float *grad_x, float *grad_s,
+                          float *grad_rho, const int32_t *bin_offsets,
+                          const int32_t *block_info, void *stream);
+
+/* Replaces HashGrid::density_gradient_backward (sph_cuda.cu:2730-2808). */
+int npa_density_gradient_backward(const npa_grid *g, const float *x_bin,
+                                  const float *mass, const float *dL_drho_grad,
+                                  float *grad_x, const int32_t *bin_offsets,
+                                  const int32_t *block_info, void *stream);
+
+/* Replaces HashGrid::moment_matrix_backward (sph_cuda.cu:2960-3046). */
+int npa_moment_matrix_backward(const npa_grid *g, const float *x_bin,
+                               const float *rho, const float *mass,
+                               const float *dL_dmoment, float *grad_x,
+                               float *grad_rho, const int32_t *bin_offsets,
+                               const int32_t *block_info, void *stream);
+
+/* out = inverse of each symmetric DxD matrix, identity when |det| < tol.
+ * n = number of matrices (B*N).  Replaces the module function
+ * safe_inv_sym_mat (sph_cuda.cu:3095-3226). */
+int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
+                         float tol, void *stream);
+
+/* ---- fused perception (one launch set for what NPA.perceive asks for) ---- *
+ * The reference runs density, blur, gradient, density_gradient and
+ * moment_matrix as separate launches that each re-stage the same neighbour
+ * cells (models/npa.py:105-126, sphops/sph.py:474-484).  These two calls
+ * produce the same tensors in two sweeps forward (rho must be complete before
+ * a neighbour's m/rho can be used) and two sweeps backward.                  */
+
+/*
+ * Forward.  Sweep 1 writes rho (required) and, when non-NULL, count and
+ * rho_grad; sweep 2 writes s_blur and s_grad (either may be NULL) and, when
+ * non-NULL, moment.  Results equal the single-operator calls above.
+ */
+int npa_perception_forward(const npa_grid *g, int32_t channels,
+                           const float *x_bin, const float *mass,
+                           const float *s_bin, float *rho, float *count,
+                           float *rho_grad, float *s_blur, float *s_grad,
+                           float *moment, const int32_t *bin_offsets,
+                           const int32_t *block_info, void *stream);
+
+/*
+ * Backward of  rho = density(x); blur(x, rho, s); gradient(x, rho, s);
+ * density_gradient(x)  as one autograd chain.  Upstream gradients dL_drho_out,
+ * dL_dblur, dL_dgrad, dL_drho_grad may each be NULL (treated as zero).
+ * Sweep 1 differentiates blur + gradient and writes grad_s, the rho gradient
+ * (into grad_rho_scratch [B,N], required when grad_x is requested) and the
+ * first part of grad_x; sweep 2 pushes (dL_drho_out + grad_rho_scratch) through
+ * density and dL_drho_grad through density_gradient and adds into grad_x.
+ * grad_x == NULL selects the cheaper variant that differentiates with respect
+ * to s only (the reference's COMPUTE_DS_ONLY kernels, sph_cuda.cu:2624,2854).
+ */
+int npa_perception_backward(const npa_grid *g, int32_t channels,
+                            const float *x_bin, const float *mass,
+                            const float *s_bin, const float *rho,
+                            const float *dL_drho_out, const float *dL_dblur,
+                            const float *dL_dgrad, const float *dL_drho_grad,
+                            float *grad_x, float *grad_s, float *grad_rho_scratch,
+                            const int32_t *bin_offsets, const int32_t *block_info,
+                            void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NPA_B200_H */

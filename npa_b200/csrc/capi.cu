@@ -1,0 +1,282 @@
+// Operator entry points of the C ABI (include/npa_b200.h): argument checks and
+// dispatch into the kernel translation units.  One function per method of the
+// reference's HashGrid class (sphops/sph_cuda.cu:2058-3046) plus the two fused
+// perception calls.
+#include "ops.cuh"
+
+namespace npa {
+
+template <int D, bool PER>
+int launch_feature_forward_geom(const Geom &, int, const FeatureFwdArgs &, cudaStream_t);
+template <int D, bool PER, bool FULL>
+int launch_feature_backward_geom(const Geom &, int, const FeatureBwdArgs &, cudaStream_t);
+
+int launch_feature_forward(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st) {
+    if (g.dim == 2)
+        return g.periodic ? launch_feature_forward_geom<2, true>(g, mask, a, st)
+                          : launch_feature_forward_geom<2, false>(g, mask, a, st);
+    return g.periodic ? launch_feature_forward_geom<3, true>(g, mask, a, st)
+                      : launch_feature_forward_geom<3, false>(g, mask, a, st);
+}
+
+int launch_feature_backward(const Geom &g, int mask, bool full, const FeatureBwdArgs &a, cudaStream_t st) {
+#define NPA_FB(DD, PP) \
+    (full ? launch_feature_backward_geom<DD, PP, true>(g, mask, a, st) \
+          : launch_feature_backward_geom<DD, PP, false>(g, mask, a, st))
+    if (g.dim == 2) return g.periodic ? NPA_FB(2, true) : NPA_FB(2, false);
+    return g.periodic ? NPA_FB(3, true) : NPA_FB(3, false);
+#undef NPA_FB
+}
+
+// Common checks of an operator call: geometry, the two snapshot arrays, the
+// positions and their vector alignment.
+static int begin_op(const char *name, const npa_grid *gd, Geom *g, const float *x,
+                    const int32_t *bin_offsets, const int32_t *block_info) {
+    int rc = make_geom(gd, g);
+    if (rc != NPA_OK) return rc;
+    if (!x) return fail(NPA_ERR_INVALID_ARGUMENT, "%s: binned_positions is NULL", name);
+    if (!bin_offsets || !block_info) return fail(NPA_ERR_INVALID_ARGUMENT, "%s: bin_offsets / block_info is NULL", name);
+    if ((uintptr_t)x % (g->dim == 2 ? 8 : 16))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "%s: binned_positions must be aligned to one position (%d bytes)", name,
+                    g->dim == 2 ? 8 : 16);
+    if ((uintptr_t)block_info % 16) return fail(NPA_ERR_INVALID_ARGUMENT, "%s: block_info must be 16-byte aligned", name);
+    return NPA_OK;
+}
+
+static int check_channels(const char *name, int C) {
+    if (C <= 0) return fail(NPA_ERR_INVALID_ARGUMENT, "%s: channels must be positive, got %d", name, C);
+    return NPA_OK;
+}
+
+static int check_grad_x(const char *name, const Geom &g, const float *grad_x) {
+    if (grad_x && (uintptr_t)grad_x % (g.dim == 2 ? 8 : 16))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "%s: grad_x must be aligned to one position", name);
+    return NPA_OK;
+}
+
+}  // namespace npa
+
+using namespace npa;
+
+#define NPA_REQUIRE(ptr, name, what) \
+    if (!(ptr)) return fail(NPA_ERR_INVALID_ARGUMENT, "%s: %s is NULL", name, what)
+
+extern "C" {
+
+int npa_count_forward(const npa_grid *gd, const float *x_bin, float *count, const int32_t *bin_offsets,
+                      const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("count_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(count, "count_forward", "count");
+    ScalarFwdArgs a = {x_bin, nullptr, nullptr, count, nullptr, nullptr, nullptr, bin_offsets, block_info};
+    return launch_scalar_forward(g, S_COUNT, a, (cudaStream_t)stream);
+}
+
+int npa_density_forward(const npa_grid *gd, const float *x_bin, const float *mass, float *rho,
+                        const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("density_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "density_forward", "rho");
+    ScalarFwdArgs a = {x_bin, mass, nullptr, nullptr, rho, nullptr, nullptr, bin_offsets, block_info};
+    return launch_scalar_forward(g, S_DENSITY, a, (cudaStream_t)stream);
+}
+
+int npa_density_gradient_forward(const npa_grid *gd, const float *x_bin, const float *mass, float *rho_grad,
+                                 const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("density_gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(rho_grad, "density_gradient_forward", "density_gradient_out");
+    ScalarFwdArgs a = {x_bin, mass, nullptr, nullptr, nullptr, rho_grad, nullptr, bin_offsets, block_info};
+    return launch_scalar_forward(g, S_DGRAD, a, (cudaStream_t)stream);
+}
+
+int npa_moment_matrix_forward(const npa_grid *gd, const float *x_bin, const float *rho, const float *mass,
+                              float *moment, const int32_t *bin_offsets, const int32_t *block_info,
+                              void *stream) {
+    Geom g;
+    int rc = begin_op("moment_matrix_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "moment_matrix_forward", "rho");
+    NPA_REQUIRE(moment, "moment_matrix_forward", "moment_matrix_out");
+    if (g.dim == 2 && (uintptr_t)moment % 16)
+        return fail(NPA_ERR_INVALID_ARGUMENT, "moment_matrix_forward: moment_matrix_out must be 16-byte aligned");
+    ScalarFwdArgs a = {x_bin, mass, rho, nullptr, nullptr, nullptr, moment, bin_offsets, block_info};
+    return launch_scalar_forward(g, S_MOMENT, a, (cudaStream_t)stream);
+}
+
+int npa_blur_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                     const float *mass, const float *s_bin, float *s_blur, const int32_t *bin_offsets,
+                     const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("blur_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("blur_forward", channels)) != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "blur_forward", "rho");
+    NPA_REQUIRE(s_bin, "blur_forward", "state_in");
+    NPA_REQUIRE(s_blur, "blur_forward", "state_out");
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, nullptr, channels, bin_offsets, block_info};
+    return launch_feature_forward(g, F_BLUR, a, (cudaStream_t)stream);
+}
+
+int npa_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                         const float *mass, const float *s_bin, float *s_grad, const int32_t *bin_offsets,
+                         const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("gradient_forward", channels)) != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "gradient_forward", "rho");
+    NPA_REQUIRE(s_bin, "gradient_forward", "state_in");
+    NPA_REQUIRE(s_grad, "gradient_forward", "state_gradient_out");
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, nullptr, s_grad, channels, bin_offsets, block_info};
+    return launch_feature_forward(g, F_GRAD, a, (cudaStream_t)stream);
+}
+
+int npa_density_backward(const npa_grid *gd, const float *x_bin, const float *mass, const float *dL_drho,
+                         float *grad_x, const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("density_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if (!grad_x) return NPA_OK;  // dLdx == false: nothing to compute (sph_cuda.cu:2519-2520)
+    NPA_REQUIRE(dL_drho, "density_backward", "dL_rho_out");
+    if ((rc = check_grad_x("density_backward", g, grad_x)) != NPA_OK) return rc;
+    ScalarBwdArgs a = {x_bin, mass, nullptr, dL_drho, nullptr, nullptr, nullptr, grad_x, nullptr, 0, bin_offsets, block_info};
+    return launch_scalar_backward(g, S_DENSITY, a, (cudaStream_t)stream);
+}
+
+int npa_density_gradient_backward(const npa_grid *gd, const float *x_bin, const float *mass,
+                                  const float *dL_drho_grad, float *grad_x, const int32_t *bin_offsets,
+                                  const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("density_gradient_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if (!grad_x) return NPA_OK;
+    NPA_REQUIRE(dL_drho_grad, "density_gradient_backward", "dL_density_gradient_out");
+    if ((rc = check_grad_x("density_gradient_backward", g, grad_x)) != NPA_OK) return rc;
+    ScalarBwdArgs a = {x_bin, mass, nullptr, nullptr, nullptr, dL_drho_grad, nullptr, grad_x, nullptr, 0, bin_offsets, block_info};
+    return launch_scalar_backward(g, S_DGRAD, a, (cudaStream_t)stream);
+}
+
+int npa_moment_matrix_backward(const npa_grid *gd, const float *x_bin, const float *rho, const float *mass,
+                               const float *dL_dmoment, float *grad_x, float *grad_rho,
+                               const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("moment_matrix_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if (!grad_x && !grad_rho) return NPA_OK;
+    NPA_REQUIRE(rho, "moment_matrix_backward", "rho");
+    NPA_REQUIRE(dL_dmoment, "moment_matrix_backward", "dL_moment_matrix_out");
+    if ((rc = check_grad_x("moment_matrix_backward", g, grad_x)) != NPA_OK) return rc;
+    ScalarBwdArgs a = {x_bin, mass, rho, nullptr, nullptr, nullptr, dL_dmoment, grad_x, grad_rho, 0, bin_offsets, block_info};
+    return launch_scalar_backward(g, S_MOMENT, a, (cudaStream_t)stream);
+}
+
+int npa_blur_backward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                      const float *mass, const float *s_bin, const float *dL_dblur, float *grad_x,
+                      float *grad_s, float *grad_rho, const int32_t *bin_offsets, const int32_t *block_info,
+                      void *stream) {
+    Geom g;
+    int rc = begin_op("blur_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("blur_backward", channels)) != NPA_OK) return rc;
+    if (!grad_x && !grad_s && !grad_rho) return NPA_OK;
+    NPA_REQUIRE(rho, "blur_backward", "rho");
+    NPA_REQUIRE(s_bin, "blur_backward", "state_in");
+    NPA_REQUIRE(dL_dblur, "blur_backward", "dL_blur_state_out");
+    if ((rc = check_grad_x("blur_backward", g, grad_x)) != NPA_OK) return rc;
+    FeatureBwdArgs a = {x_bin, mass, rho, s_bin, dL_dblur, nullptr, grad_x, grad_s, grad_rho, channels, bin_offsets, block_info};
+    return launch_feature_backward(g, F_BLUR, grad_x || grad_rho, a, (cudaStream_t)stream);
+}
+
+int npa_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                          const float *mass, const float *s_bin, const float *dL_dgrad, float *grad_x,
+                          float *grad_s, float *grad_rho, const int32_t *bin_offsets,
+                          const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("gradient_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("gradient_backward", channels)) != NPA_OK) return rc;
+    if (!grad_x && !grad_s && !grad_rho) return NPA_OK;
+    NPA_REQUIRE(rho, "gradient_backward", "rho");
+    NPA_REQUIRE(s_bin, "gradient_backward", "state_in");
+    NPA_REQUIRE(dL_dgrad, "gradient_backward", "dL_grad_state_out");
+    if ((rc = check_grad_x("gradient_backward", g, grad_x)) != NPA_OK) return rc;
+    FeatureBwdArgs a = {x_bin, mass, rho, s_bin, nullptr, dL_dgrad, grad_x, grad_s, grad_rho, channels, bin_offsets, block_info};
+    return launch_feature_backward(g, F_GRAD, grad_x || grad_rho, a, (cudaStream_t)stream);
+}
+
+int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *mass,
+                           const float *s_bin, float *rho, float *count, float *rho_grad, float *s_blur,
+                           float *s_grad, float *moment, const int32_t *bin_offsets,
+                           const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("perception_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "perception_forward", "rho");
+    cudaStream_t st = (cudaStream_t)stream;
+    int smask = S_DENSITY | (count ? S_COUNT : 0) | (rho_grad ? S_DGRAD : 0);
+    ScalarFwdArgs sa = {x_bin, mass, nullptr, count, rho, rho_grad, nullptr, bin_offsets, block_info};
+    if ((rc = launch_scalar_forward(g, smask, sa, st)) != NPA_OK) return rc;
+    const int fmask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
+    if (fmask) {
+        if ((rc = check_channels("perception_forward", channels)) != NPA_OK) return rc;
+        NPA_REQUIRE(s_bin, "perception_forward", "state_in");
+        FeatureFwdArgs fa = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info};
+        if ((rc = launch_feature_forward(g, fmask, fa, st)) != NPA_OK) return rc;
+    }
+    if (moment) {
+        if (g.dim == 2 && (uintptr_t)moment % 16)
+            return fail(NPA_ERR_INVALID_ARGUMENT, "perception_forward: moment must be 16-byte aligned");
+        ScalarFwdArgs ma = {x_bin, mass, rho, nullptr, nullptr, nullptr, moment, bin_offsets, block_info};
+        if ((rc = launch_scalar_forward(g, S_MOMENT, ma, st)) != NPA_OK) return rc;
+    }
+    return NPA_OK;
+}
+
+int npa_perception_backward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *mass,
+                            const float *s_bin, const float *rho, const float *dL_drho_out,
+                            const float *dL_dblur, const float *dL_dgrad, const float *dL_drho_grad,
+                            float *grad_x, float *grad_s, float *grad_rho_scratch,
+                            const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("perception_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_grad_x("perception_backward", g, grad_x)) != NPA_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int fmask = (dL_dblur ? F_BLUR : 0) | (dL_dgrad ? F_GRAD : 0);
+    const bool full = grad_x != nullptr;
+    if (full && fmask && !grad_rho_scratch)
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perception_backward: grad_rho_scratch is required when grad_x is requested");
+    bool x_written = false;
+    if (fmask && (grad_s || full)) {
+        if ((rc = check_channels("perception_backward", channels)) != NPA_OK) return rc;
+        NPA_REQUIRE(s_bin, "perception_backward", "state_in");
+        NPA_REQUIRE(rho, "perception_backward", "rho");
+        FeatureBwdArgs fa = {x_bin, mass, rho, s_bin, dL_dblur, dL_dgrad, grad_x, grad_s,
+                             full ? grad_rho_scratch : nullptr, channels, bin_offsets, block_info};
+        if ((rc = launch_feature_backward(g, fmask, full, fa, st)) != NPA_OK) return rc;
+        x_written = full;
+    } else if (grad_s) {
+        cudaError_t e = cudaMemsetAsync(grad_s, 0, sizeof(float) * (size_t)g.B * g.N * (channels > 0 ? channels : 0), st);
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaMemsetAsync(grad_s): %s", cudaGetErrorString(e));
+    }
+    if (full) {
+        const float *ga = dL_drho_out;
+        const float *gb = x_written ? grad_rho_scratch : nullptr;
+        const int smask = ((ga || gb) ? S_DENSITY : 0) | (dL_drho_grad ? S_DGRAD : 0);
+        if (smask) {
+            ScalarBwdArgs sa = {x_bin, mass, nullptr, ga, gb, dL_drho_grad, nullptr, grad_x, nullptr,
+                                x_written ? 1 : 0, bin_offsets, block_info};
+            if ((rc = launch_scalar_backward(g, smask, sa, st)) != NPA_OK) return rc;
+        } else if (!x_written) {
+            cudaError_t e = cudaMemsetAsync(grad_x, 0, sizeof(float) * (size_t)g.B * g.N * (g.dim == 2 ? 2 : 4), st);
+            if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaMemsetAsync(grad_x): %s", cudaGetErrorString(e));
+        }
+    }
+    return NPA_OK;
+}
+
+}  // extern "C"

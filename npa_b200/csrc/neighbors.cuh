@@ -1,0 +1,152 @@
+// Neighbour enumeration shared by every perception kernel.
+//
+// One warp owns one work item (a row of block_info: <= MPB particles of one
+// cell).  The warp first turns the 3^D neighbour cells into a short list of
+// contiguous particle ranges: with the linear hash the three x-adjacent cells
+// of a (y, z) row are contiguous in cell order (the observation the reference's
+// block-per-cell kernel is built on, sphops/sph_cuda.cu:1561-1660), so a row is
+// one range, or two when a periodic row wraps; with the Morton hash each cell is
+// its own range.  The warp is split into sub-groups of LPP lanes; each sub-group
+// owns one particle i of the item and its lanes test LPP candidates j per round.
+#pragma once
+#include "common.cuh"
+
+namespace npa {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kMaxRanges = 28;
+
+struct WorkItem {
+    int first;  // global index of the item's first particle (cell order)
+    int count;  // particles in the item, 0 = unused row
+    int cell;   // global cell index (system * cells + hash)
+    int sys;    // system (batch) index
+};
+
+__device__ inline WorkItem load_item(const int32_t *__restrict__ block_info,
+                                     const int32_t *__restrict__ bin_offsets, int row) {
+    const int4 rec = __ldg(reinterpret_cast<const int4 *>(block_info) + row);
+    WorkItem it;
+    it.cell = rec.x;
+    it.count = rec.z;
+    it.sys = rec.w;
+    it.first = rec.z > 0 ? __ldg(bin_offsets + rec.x) + rec.y : 0;
+    return it;
+}
+
+// Neighbour coordinate along one axis; false when the clamped grid ends there
+// or when a small periodic axis would visit the same cell twice.
+__device__ inline bool neighbor_axis(int c, int o, int n, int periodic, int &out) {
+    if (!periodic) {
+        out = c + o;
+        return out >= 0 && out < n;
+    }
+    if (n == 1) {
+        out = c;
+        return o == 0;
+    }
+    if (n == 2) {
+        out = (c + o) & 1;
+        return o >= 0;
+    }
+    out = c + o;
+    out = out < 0 ? out + n : (out >= n ? out - n : out);
+    return true;
+}
+
+// Fills rng[0..n) with the non-empty candidate ranges [start, end) of global
+// particle indices for the cell of `it`; returns n.  Must be called by all 32
+// lanes; rng is per-warp shared memory of kMaxRanges entries.
+template <int D>
+__device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bin_offsets,
+                                   const WorkItem &it, int2 *rng) {
+    const int lane = threadIdx.x & 31;
+    int cx, cy, cz;
+    hash_to_cell<D>(g, (uint32_t)(it.cell - it.sys * g.cells), cx, cy, cz);
+    const int32_t *off = bin_offsets + (size_t)it.sys * g.cells;
+    int start = 0, end = 0;
+    if (!g.morton) {
+        const int row = lane >> 1, piece = lane & 1;
+        if (row < (D == 2 ? 3 : 9)) {
+            int ny = 0, nz = 0;
+            bool ok = neighbor_axis(cy, row % 3 - 1, g.g[1], g.periodic, ny);
+            if (D == 3) ok = neighbor_axis(cz, row / 3 - 1, g.g[2], g.periodic, nz) && ok;
+            const int gx = g.g[0];
+            int xlo = 0, xhi = -1;
+            if (!g.periodic) {
+                if (piece == 0) { xlo = max(cx - 1, 0); xhi = min(cx + 1, gx - 1); }
+            } else if (gx <= 3) {
+                if (piece == 0) { xlo = 0; xhi = gx - 1; }
+            } else if (cx == 0) {
+                if (piece == 0) { xlo = 0; xhi = 1; } else { xlo = xhi = gx - 1; }
+            } else if (cx == gx - 1) {
+                if (piece == 0) { xlo = gx - 2; xhi = gx - 1; } else { xlo = xhi = 0; }
+            } else if (piece == 0) {
+                xlo = cx - 1; xhi = cx + 1;
+            }
+            if (ok && xhi >= xlo) {
+                start = __ldg(off + cell_hash<D>(g, xlo, ny, nz));
+                end = __ldg(off + cell_hash<D>(g, xhi, ny, nz) + 1);
+            }
+        }
+    } else {
+        if (lane < (D == 2 ? 9 : 27)) {
+            int nx = 0, ny = 0, nz = 0;
+            bool ok = neighbor_axis(cx, lane % 3 - 1, g.g[0], g.periodic, nx);
+            ok = neighbor_axis(cy, (lane / 3) % 3 - 1, g.g[1], g.periodic, ny) && ok;
+            if (D == 3) ok = neighbor_axis(cz, lane / 9 - 1, g.g[2], g.periodic, nz) && ok;
+            if (ok) {
+                const uint32_t hsh = cell_hash<D>(g, nx, ny, nz);
+                start = __ldg(off + hsh);
+                end = __ldg(off + hsh + 1);
+            }
+        }
+    }
+    const bool nonempty = end > start;
+    const unsigned m = __ballot_sync(kFull, nonempty);
+    if (nonempty) rng[__popc(m & ((1u << lane) - 1))] = make_int2(start, end);
+    __syncwarp();
+    return __popc(m);
+}
+
+template <int D>
+struct Pos {
+    float x, y, z;
+};
+
+template <int D>
+__device__ inline Pos<D> load_pos(const float *__restrict__ x, long long idx) {
+    Pos<D> p;
+    if (D == 2) {
+        const float2 v = __ldg(reinterpret_cast<const float2 *>(x) + idx);
+        p.x = v.x; p.y = v.y; p.z = 0.f;
+    } else {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + idx);
+        p.x = v.x; p.y = v.y; p.z = v.z;
+    }
+    return p;
+}
+
+// r = x_j - x_i (minimum image when PER) and q = |r|^2.
+template <int D, bool PER>
+__device__ inline float displacement(const Geom &g, const Pos<D> &pi, const Pos<D> &pj, float &rx, float &ry, float &rz) {
+    rx = pj.x - pi.x;
+    ry = pj.y - pi.y;
+    rz = D == 3 ? pj.z - pi.z : 0.f;
+    if (PER) {
+        rx = min_image(rx, g.L[0], g.invL[0]);
+        ry = min_image(ry, g.L[1], g.invL[1]);
+        if (D == 3) rz = min_image(rz, g.L[2], g.invL[2]);
+    }
+    return sq_norm<D>(rx, ry, rz);
+}
+
+// Sum over the LPP lanes of a sub-group (LPP a power of two <= 32).
+template <int LPP>
+__device__ inline float subgroup_sum(float v) {
+#pragma unroll
+    for (int o = LPP >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+}  // namespace npa

@@ -1,0 +1,73 @@
+// Argument blocks and launch functions of the perception kernels; the glue
+// between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+#include "common.cuh"
+
+namespace npa {
+
+// Which per-particle scalar operators a sweep computes.
+enum { S_COUNT = 1, S_DENSITY = 2, S_DGRAD = 4, S_MOMENT = 8 };
+// Which feature operators a sweep computes.
+enum { F_BLUR = 1, F_GRAD = 2 };
+
+struct ScalarFwdArgs {
+    const float *x;       // [B,N,P] cell order
+    const float *mass;    // [B,N] or NULL (all ones)
+    const float *rho_in;  // [B,N], only for S_MOMENT
+    float *count;         // [B,N]
+    float *rho_out;       // [B,N]
+    float *rho_grad;      // [B,N,D]
+    float *moment;        // [B,N,D,D]
+    const int32_t *bin_offsets;
+    const int32_t *block_info;
+};
+
+struct ScalarBwdArgs {
+    const float *x;
+    const float *mass;
+    const float *rho_in;      // S_MOMENT
+    const float *g_rho_a;     // upstream of density output; the two are summed, either may be NULL
+    const float *g_rho_b;
+    const float *g_rho_grad;  // upstream of density gradient [B,N,D]
+    const float *g_moment;    // upstream of moment matrix [B,N,D,D]
+    float *grad_x;            // [B,N,P]
+    float *grad_rho;          // [B,N], S_MOMENT only
+    int accumulate_x;         // add into grad_x instead of overwriting
+    const int32_t *bin_offsets;
+    const int32_t *block_info;
+};
+
+struct FeatureFwdArgs {
+    const float *x;
+    const float *mass;
+    const float *rho;
+    const float *s;      // [B,N,C]
+    float *blur;         // [B,N,C]
+    float *grad;         // [B,N,C,D]
+    int C;
+    const int32_t *bin_offsets;
+    const int32_t *block_info;
+};
+
+struct FeatureBwdArgs {
+    const float *x;
+    const float *mass;
+    const float *rho;
+    const float *s;
+    const float *g_blur;  // [B,N,C]
+    const float *g_grad;  // [B,N,C,D]
+    float *grad_x;        // [B,N,P] or NULL
+    float *grad_s;        // [B,N,C] or NULL
+    float *grad_rho;      // [B,N] or NULL
+    int C;
+    const int32_t *bin_offsets;
+    const int32_t *block_info;
+};
+
+int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st);
+int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st);
+int launch_feature_forward(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st);
+// full = false differentiates with respect to s only.
+int launch_feature_backward(const Geom &g, int mask, bool full, const FeatureBwdArgs &a, cudaStream_t st);
+
+}  // namespace npa

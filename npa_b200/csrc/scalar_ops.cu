@@ -1,0 +1,295 @@
+// Per-particle scalar SPH operators: count, density, density gradient and
+// moment matrix, forward and backward, on the warp-per-work-item neighbour
+// walk of neighbors.cuh.  Any subset of the four runs fused in one sweep.
+//
+// Replaces forward_kernel / backward_kernel of the reference for the
+// Count, Density, DensityGradient and MomentMatrix computation types
+// (sphops/sph_cuda.cu:1418-1812 and 723-1416; pair math at :1160-1184,
+// :1236-1264, :1328-1375).  The backward is a gather: particle i accumulates
+// the terms of both roles it plays in a pair, so no global atomics are needed.
+#include "neighbors.cuh"
+#include "ops.cuh"
+
+namespace npa {
+
+constexpr int kScalarLpp = 4;                  // lanes per particle
+constexpr int kScalarPpw = 32 / kScalarLpp;    // particles per warp pass
+
+template <int D, bool PER, int MASK>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
+    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerCta + warp;
+    if (row >= g.max_blocks) return;
+    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+    if (it.count <= 0) return;
+    int2 *rng = s_ranges[warp];
+    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+    const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
+    constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
+    constexpr bool kPoly = (MASK & S_DENSITY) != 0;
+    constexpr int kSym = D * (D + 1) / 2;
+
+    for (int k0 = 0; k0 < it.count; k0 += kScalarPpw) {
+        const int k = k0 + sub;
+        const bool ivalid = k < it.count;
+        const long long i = it.first + (ivalid ? k : 0);
+        const Pos<D> pi = load_pos<D>(a.x, i);
+        float cnt = 0.f, rho = 0.f, dg[3] = {0.f, 0.f, 0.f}, mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < nr; ++r) {
+            const int2 rg = rng[r];
+            for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
+                const int j = j0 + sl;
+                if (!(ivalid && j < rg.y)) continue;
+                const Pos<D> pj = load_pos<D>(a.x, j);
+                float rx, ry, rz;
+                const float q = displacement<D, PER>(g, pi, pj, rx, ry, rz);
+                if (!(q < g.h2)) continue;
+                if (MASK & S_COUNT) cnt += 1.0f;
+                const float mj = (kPoly || kSpiky) ? (a.mass ? __ldg(a.mass + j) : 1.0f) : 0.f;
+                if (kPoly) {
+                    const float t = fmaxf(g.h2 - q, 0.f);
+                    rho = fmaf(mj, t * t * t, rho);
+                }
+                if (kSpiky && q > 0.f) {
+                    float d;
+                    const float phi = spiky_phi(q, g.h, d);
+                    if (MASK & S_DGRAD) {
+                        const float w = mj * phi;
+                        dg[0] = fmaf(w, rx, dg[0]);
+                        dg[1] = fmaf(w, ry, dg[1]);
+                        if (D == 3) dg[2] = fmaf(w, rz, dg[2]);
+                    }
+                    if (MASK & S_MOMENT) {
+                        const float w = phi * mj / __ldg(a.rho_in + j);
+                        mom[0] = fmaf(w * rx, rx, mom[0]);
+                        mom[1] = fmaf(w * rx, ry, mom[1]);
+                        if (D == 2) {
+                            mom[2] = fmaf(w * ry, ry, mom[2]);
+                        } else {
+                            mom[2] = fmaf(w * rx, rz, mom[2]);
+                            mom[3] = fmaf(w * ry, ry, mom[3]);
+                            mom[4] = fmaf(w * ry, rz, mom[4]);
+                            mom[5] = fmaf(w * rz, rz, mom[5]);
+                        }
+                    }
+                }
+            }
+        }
+        // sub-group reduction (all 32 lanes take part) and write-out by lane 0 of each sub-group
+        if (MASK & S_COUNT) cnt = subgroup_sum<kScalarLpp>(cnt);
+        if (kPoly) rho = subgroup_sum<kScalarLpp>(rho);
+        if (MASK & S_DGRAD)
+#pragma unroll
+            for (int d = 0; d < D; ++d) dg[d] = subgroup_sum<kScalarLpp>(dg[d]);
+        if (MASK & S_MOMENT)
+#pragma unroll
+            for (int d = 0; d < kSym; ++d) mom[d] = subgroup_sum<kScalarLpp>(mom[d]);
+        if (ivalid && sl == 0) {
+            if ((MASK & S_COUNT) && a.count) a.count[i] = cnt;
+            if (kPoly && a.rho_out) a.rho_out[i] = g.c_s * rho;
+            if ((MASK & S_DGRAD) && a.rho_grad) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) a.rho_grad[i * D + d] = g.c_g * dg[d];
+            }
+            if ((MASK & S_MOMENT) && a.moment) {
+                float *o = a.moment + i * (D * D);
+                if (D == 2) {
+                    reinterpret_cast<float4 *>(o)[0] =
+                        make_float4(g.c_g * mom[0], g.c_g * mom[1], g.c_g * mom[1], g.c_g * mom[2]);
+                } else {
+                    o[0] = g.c_g * mom[0]; o[1] = g.c_g * mom[1]; o[2] = g.c_g * mom[2];
+                    o[3] = g.c_g * mom[1]; o[4] = g.c_g * mom[3]; o[5] = g.c_g * mom[4];
+                    o[6] = g.c_g * mom[2]; o[7] = g.c_g * mom[4]; o[8] = g.c_g * mom[5];
+                }
+            }
+        }
+    }
+}
+
+// dK/dr applied to u:  J u = phi u - psi (r.u) r.
+template <int D>
+__device__ inline void apply_jacobian(float phi, float psi, float rx, float ry, float rz,
+                                      float ux, float uy, float uz, float &ox, float &oy, float &oz) {
+    float ru = rx * ux + ry * uy;
+    if (D == 3) ru = fmaf(rz, uz, ru);
+    const float s = psi * ru;
+    ox = phi * ux - s * rx;
+    oy = phi * uy - s * ry;
+    oz = D == 3 ? phi * uz - s * rz : 0.f;
+}
+
+template <int D, bool PER, int MASK>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
+    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kWarpsPerCta + warp;
+    if (row >= g.max_blocks) return;
+    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+    if (it.count <= 0) return;
+    int2 *rng = s_ranges[warp];
+    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+    const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
+    constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
+    constexpr int DD = D * D;
+
+    for (int k0 = 0; k0 < it.count; k0 += kScalarPpw) {
+        const int k = k0 + sub;
+        const bool ivalid = k < it.count;
+        const long long i = it.first + (ivalid ? k : 0);
+        const Pos<D> pi = load_pos<D>(a.x, i);
+        const float mi = a.mass ? __ldg(a.mass + i) : 1.0f;
+        float gri = 0.f, gdi[3] = {0.f, 0.f, 0.f}, gmi[DD], vi = 0.f;
+        if (MASK & S_DENSITY) {
+            if (a.g_rho_a) gri += __ldg(a.g_rho_a + i);
+            if (a.g_rho_b) gri += __ldg(a.g_rho_b + i);
+        }
+        if (MASK & S_DGRAD)
+#pragma unroll
+            for (int d = 0; d < D; ++d) gdi[d] = __ldg(a.g_rho_grad + i * D + d);
+        if (MASK & S_MOMENT) {
+#pragma unroll
+            for (int d = 0; d < DD; ++d) gmi[d] = __ldg(a.g_moment + i * DD + d);
+            vi = mi / __ldg(a.rho_in + i);
+        }
+        float dxs[3] = {0.f, 0.f, 0.f};  // poly6 part, scaled by c_s at the end
+        float dxg[3] = {0.f, 0.f, 0.f};  // spiky part, scaled by c_g at the end
+        float drho = 0.f;
+        for (int r = 0; r < nr; ++r) {
+            const int2 rg = rng[r];
+            for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
+                const long long j = j0 + sl;
+                if (!(ivalid && j < rg.y)) continue;
+                const Pos<D> pj = load_pos<D>(a.x, j);
+                float rv[3];
+                const float q = displacement<D, PER>(g, pi, pj, rv[0], rv[1], rv[2]);
+                if (!(q < g.h2) || !(q > 0.f)) continue;  // the self / coincident pair has zero gradient
+                const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
+                if (MASK & S_DENSITY) {
+                    float grj = 0.f;
+                    if (a.g_rho_a) grj += __ldg(a.g_rho_a + j);
+                    if (a.g_rho_b) grj += __ldg(a.g_rho_b + j);
+                    const float t = fmaxf(g.h2 - q, 0.f);
+                    const float w = 6.0f * t * t * (gri * mj + grj * mi);
+#pragma unroll
+                    for (int d = 0; d < D; ++d) dxs[d] = fmaf(w, rv[d], dxs[d]);
+                }
+                if (kSpiky) {
+                    float dist;
+                    const float phi = spiky_phi(q, g.h, dist);
+                    const float psi = spiky_psi(dist, g.h);
+                    if (MASK & S_DGRAD) {
+                        float u[3] = {0.f, 0.f, 0.f}, o[3];
+#pragma unroll
+                        for (int d = 0; d < D; ++d) u[d] = mi * __ldg(a.g_rho_grad + j * D + d) - mj * gdi[d];
+                        apply_jacobian<D>(phi, psi, rv[0], rv[1], rv[2], u[0], u[1], u[2], o[0], o[1], o[2]);
+#pragma unroll
+                        for (int d = 0; d < D; ++d) dxg[d] += o[d];
+                    }
+                    if (MASK & S_MOMENT) {
+                        const float vj = mj / __ldg(a.rho_in + j);
+                        float w[3] = {0.f, 0.f, 0.f}, o[3];
+                        float rr = 0.f;  // sum_ab gM_j[a,b] r_a r_b
+#pragma unroll
+                        for (int p = 0; p < D; ++p) {
+                            float kc = 0.f;  // sum_b Cm[p,b] K_b
+#pragma unroll
+                            for (int b = 0; b < D; ++b) {
+                                const float gj = __ldg(a.g_moment + j * DD + p * D + b);
+                                const float cm = vj * gmi[p * D + b] + vi * gj;
+                                kc = fmaf(cm, phi * rv[b], kc);
+                                w[b] = fmaf(rv[p], cm, w[b]);
+                                rr = fmaf(gj * rv[p], rv[b], rr);
+                            }
+                            dxg[p] -= kc;
+                        }
+                        apply_jacobian<D>(phi, psi, rv[0], rv[1], rv[2], w[0], w[1], w[2], o[0], o[1], o[2]);
+#pragma unroll
+                        for (int d = 0; d < D; ++d) dxg[d] -= o[d];
+                        drho = fmaf(rr, phi, drho);
+                    }
+                }
+            }
+        }
+        float out[3];
+#pragma unroll
+        for (int d = 0; d < D; ++d)
+            out[d] = subgroup_sum<kScalarLpp>(g.c_s * dxs[d] + g.c_g * dxg[d]);
+        if (MASK & S_MOMENT) drho = subgroup_sum<kScalarLpp>(drho);
+        if (ivalid && sl == 0) {
+            if (a.grad_x) {
+                if (D == 2) {
+                    float2 *o = reinterpret_cast<float2 *>(a.grad_x) + i;
+                    float2 v = make_float2(out[0], out[1]);
+                    if (a.accumulate_x) { const float2 p = *o; v.x += p.x; v.y += p.y; }
+                    *o = v;
+                } else {
+                    float4 *o = reinterpret_cast<float4 *>(a.grad_x) + i;
+                    float4 v = make_float4(out[0], out[1], out[2], 0.f);
+                    if (a.accumulate_x) { const float4 p = *o; v.x += p.x; v.y += p.y; v.z += p.z; }
+                    *o = v;
+                }
+            }
+            if ((MASK & S_MOMENT) && a.grad_rho) a.grad_rho[i] = -g.c_g * (vi * vi / mi) * drho;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dispatch
+// ---------------------------------------------------------------------------
+template <int MASK>
+static int launch_scalar_fwd_mask(const Geom &g, const ScalarFwdArgs &a, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
+    const unsigned threads = kWarpsPerCta * 32;
+    if (g.dim == 2) {
+        if (g.periodic) scalar_forward_kernel<2, true, MASK><<<blocks, threads, 0, st>>>(a, g);
+        else scalar_forward_kernel<2, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+    } else {
+        if (g.periodic) scalar_forward_kernel<3, true, MASK><<<blocks, threads, 0, st>>>(a, g);
+        else scalar_forward_kernel<3, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+    }
+    return check_launch("scalar_forward_kernel");
+}
+
+int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st) {
+    switch (mask) {
+        case S_COUNT: return launch_scalar_fwd_mask<S_COUNT>(g, a, st);
+        case S_DENSITY: return launch_scalar_fwd_mask<S_DENSITY>(g, a, st);
+        case S_DGRAD: return launch_scalar_fwd_mask<S_DGRAD>(g, a, st);
+        case S_MOMENT: return launch_scalar_fwd_mask<S_MOMENT>(g, a, st);
+        case S_DENSITY | S_DGRAD: return launch_scalar_fwd_mask<S_DENSITY | S_DGRAD>(g, a, st);
+        default:
+            if ((mask & ~(S_COUNT | S_DENSITY | S_DGRAD)) == 0)
+                return launch_scalar_fwd_mask<S_COUNT | S_DENSITY | S_DGRAD>(g, a, st);
+            return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported scalar forward mask %d", mask);
+    }
+}
+
+template <int MASK>
+static int launch_scalar_bwd_mask(const Geom &g, const ScalarBwdArgs &a, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
+    const unsigned threads = kWarpsPerCta * 32;
+    if (g.dim == 2) {
+        if (g.periodic) scalar_backward_kernel<2, true, MASK><<<blocks, threads, 0, st>>>(a, g);
+        else scalar_backward_kernel<2, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+    } else {
+        if (g.periodic) scalar_backward_kernel<3, true, MASK><<<blocks, threads, 0, st>>>(a, g);
+        else scalar_backward_kernel<3, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+    }
+    return check_launch("scalar_backward_kernel");
+}
+
+int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st) {
+    switch (mask) {
+        case S_DENSITY: return launch_scalar_bwd_mask<S_DENSITY>(g, a, st);
+        case S_DGRAD: return launch_scalar_bwd_mask<S_DGRAD>(g, a, st);
+        case S_MOMENT: return launch_scalar_bwd_mask<S_MOMENT>(g, a, st);
+        case S_DENSITY | S_DGRAD: return launch_scalar_bwd_mask<S_DENSITY | S_DGRAD>(g, a, st);
+        default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported scalar backward mask %d", mask);
+    }
+}
+
+}  // namespace npa

@@ -1,0 +1,77 @@
+"""Pins the C oracle (oracle/sph_oracle.c) to the reference's own operators.
+
+The fixtures were produced by importing the reference's sphops/torch_sph.py
+(tests/golden/make_golden.py).  The oracle accumulates in double, so it must
+agree with the fp64 run to rounding, and with the fp32 run to fp32 accuracy.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import assert_close, golden_names, load_golden
+
+FWD = ["rho", "rho_grad", "blur", "grad", "moment"]
+
+
+def _inputs(meta, arr):
+    box = [g * meta["eps"] for g in meta["grid"]] if meta["periodic"] else None
+    kw = dict(mass=arr.get("in_mass"), s=arr["in_s"], rho_in=arr["in_rho_in"],
+              periodic=meta["periodic"], box_size=box)
+    return arr["in_x"], kw
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_forward_matches_reference(name):
+    meta, arr = load_golden(name)
+    x, kw = _inputs(meta, arr)
+    out = oracle.forward(x, meta["eps"], meta["dim"], want=("count", *FWD), **kw)
+    # count is evaluated with the reference's fp32 arithmetic: exact
+    np.testing.assert_array_equal(out["count"], arr["f32_count"])
+    for k in FWD:
+        assert_close(out[k], arr[f"f64_{k}"], rtol=1e-9, atol_scale=1e-11, what=f"{name}:{k} vs fp64")
+        assert_close(out[k], arr[f"f32_{k}"], rtol=1e-4, atol_scale=2e-6, what=f"{name}:{k} vs fp32")
+
+
+@pytest.mark.parametrize("name", golden_names())
+@pytest.mark.parametrize("op,up", [("density", "g_rho"), ("rho_grad", "g_rho_grad"), ("blur", "g_blur"),
+                                   ("grad", "g_grad"), ("moment", "g_moment")])
+def test_backward_matches_reference_autograd(name, op, up):
+    meta, arr = load_golden(name)
+    x, kw = _inputs(meta, arr)
+    dx, ds, drho = oracle.backward(x, meta["eps"], meta["dim"], **kw, **{up: arr[f"in_{up}"]})
+    assert_close(dx, arr[f"f64_bw_{op}_dx"], rtol=1e-8, atol_scale=1e-10, what=f"{name}:{op} dx")
+    if f"f64_bw_{op}_ds" in arr:
+        assert_close(ds, arr[f"f64_bw_{op}_ds"], rtol=1e-8, atol_scale=1e-10, what=f"{name}:{op} ds")
+    if f"f64_bw_{op}_drho" in arr:
+        assert_close(drho, arr[f"f64_bw_{op}_drho"], rtol=1e-8, atol_scale=1e-10, what=f"{name}:{op} drho")
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_chained_backward_matches_reference_autograd(name):
+    """rho = density(x) feeding blur and gradient: two oracle calls composed as autograd does."""
+    meta, arr = load_golden(name)
+    x, kw = _inputs(meta, arr)
+    kw = dict(kw)
+    # the chain differentiates through the density the operators were fed, i.e. torch's own rho;
+    # the fixture's chain used rho computed in the run's dtype, so feed the fp64 truth rounded once
+    kw["rho_in"] = arr["f64_rho"].astype(np.float32)
+    dx1, ds, drho = oracle.backward(x, meta["eps"], meta["dim"], **kw,
+                                    g_blur=arr["in_g_blur"], g_grad=arr["in_g_grad"])
+    g_rho_total = (arr["in_g_rho"].astype(np.float64) + drho).astype(np.float32)
+    kw2 = dict(kw, s=None, rho_in=None)
+    dx2, _, _ = oracle.backward(x, meta["eps"], meta["dim"], **kw2, g_rho=g_rho_total,
+                                g_rho_grad=arr["in_g_rho_grad"])
+    # rho rounded to fp32 and the fp32 hand-over of drho bound the agreement
+    assert_close(dx1 + dx2, arr["f64_chain_dx"], rtol=2e-5, atol_scale=2e-6, what=f"{name}: chain dx")
+    assert_close(ds, arr["f64_chain_ds"], rtol=2e-5, atol_scale=2e-6, what=f"{name}: chain ds")
+
+
+def test_safe_inverse_identity_fallback():
+    rng = np.random.default_rng(0)
+    for dim in (2, 3):
+        a = rng.standard_normal((50, dim, dim)).astype(np.float32)
+        m = a @ a.transpose(0, 2, 1) + 0.5 * np.eye(dim, dtype=np.float32)
+        m[0] = 0.0  # singular -> identity
+        inv = oracle.safe_inv_sym_mat(m, 1e-3)
+        np.testing.assert_array_equal(inv[0], np.eye(dim, dtype=np.float32))
+        np.testing.assert_allclose(inv[1:] @ m[1:], np.broadcast_to(np.eye(dim), (49, dim, dim)), atol=2e-4)
