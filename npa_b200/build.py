@@ -70,7 +70,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         objs = list(pool.map(lambda s: _compile(s, verbose or ptxas_info, extra), sources))
     if (not LIB_PATH.exists()) or any(o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs):
         cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-o", str(LIB_PATH), *map(str, objs), "-lcudart"]
+               "-cudart", "static", "-o", str(LIB_PATH), *map(str, objs)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

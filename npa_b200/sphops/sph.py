@@ -1,0 +1,373 @@
+"""The ``sphops`` operator API on top of the B200 kernels.
+
+Same public names, signatures, defaults and autograd behaviour as the
+reference's ``sphops/sph.py`` (HashGrid :42-123, Permute :127-184,
+unbin_particles :187-198, Count :201-229, Density :232-267, Blur :270-321,
+Gradient :324-376, DensityGradient :379-413, MomentMatrix :416-464,
+safe_inv_sym_mat :467-471, gradient_hybrid :474-484), so ``models/npa.py`` and
+the trainers of the reference run unchanged on it.  Two additions that the
+reference does not have: :func:`perceive`, the fused forward/backward of the
+whole perception step, and the ``device`` argument of :class:`HashGrid`.
+
+Semantics kept from the reference: default mass is 1.0 per particle; ``rho`` is
+a density and the operators form ``mass / rho`` themselves; 3D positions are
+``[B, N, 4]`` with an ignored fourth column whose gradient is 0; gradients of
+inputs that do not require grad are returned as ``None``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import sph_cuda
+
+
+def _default_mass(x, mass):
+    if mass is None:
+        B, N, _ = x.shape
+        return x.new_full((B, N), 1.0)
+    if mass.dim() == 3 and mass.shape[-1] == 1:
+        return mass.squeeze(-1)
+    return mass
+
+
+_GRID_CLASSES = {
+    (2, "periodic", "grid"): "HashGrid2DPeriodic",
+    (3, "periodic", "grid"): "HashGrid3DPeriodic",
+    (2, "clamped", "grid"): "HashGrid2DBox",
+    (3, "clamped", "grid"): "HashGrid3DBox",
+    (2, "periodic", "particle"): "VHashGrid2DPeriodic",
+    (3, "periodic", "particle"): "VHashGrid3DPeriodic",
+    (2, "clamped", "particle"): "VHashGrid2DBox",
+    (3, "clamped", "particle"): "VHashGrid3DBox",
+}
+
+
+def get_hashgrid_cls(dim, boundary, mode):
+    return getattr(sph_cuda, _GRID_CLASSES[(dim, boundary, mode)])
+
+
+@dataclass
+class HashGridSnapshot:
+    """Result of one binning pass; every tensor a later operator needs lives here."""
+
+    grid: object
+    bin_offsets: torch.Tensor
+    permutation: torch.Tensor
+    block_info: torch.Tensor
+    dim: int
+
+
+class HashGrid:
+    """Uniform grid over ``[-G*eps/2, G*eps/2)`` per axis, cell size = cut-off ``eps``.
+
+    ``mode="grid"`` orders cells linearly, ``mode="particle"`` along a Morton
+    curve (power-of-two sizes only); both run the same kernels here.
+    ``max_particles_per_block`` bounds the particles of one work item.
+    """
+
+    def __init__(self, dim=2, boundary="periodic", mode="grid", grid_size=(16, 16), eps=0.1,
+                 num_particles=4096, batch_size=8, max_particles_per_block=64, device=None):
+        self.dim = dim
+        self.boundary = boundary
+        self.mode = mode
+        self.grid_size = grid_size
+        self.eps = eps
+        self.num_particles = num_particles
+        self.batch_size = batch_size
+        self.max_particles_per_block = max_particles_per_block
+        if mode == "particle":
+            for size in grid_size:
+                assert (size & (size - 1)) == 0, "grid_size must be a power of 2"
+        self.num_cells = math.prod(grid_size)
+        self.hashgrid_cls = get_hashgrid_cls(dim, boundary, mode)
+        self.hashgrid = self.hashgrid_cls(*grid_size, eps, num_particles, batch_size, max_particles_per_block)
+        self.device = torch.device("cuda") if device is None else torch.device(device)
+
+    def instantiate(self, x):
+        """Bin positions ``x [B, N, P]`` and return the snapshot the operators take."""
+        B, N, _ = x.shape
+        dev = x.device if x.is_cuda else self.device
+        permutation = torch.empty(B, N, dtype=torch.int32, device=dev)
+        bin_offsets = torch.empty(B * self.num_cells + 1, dtype=torch.int32, device=dev)
+        block_info = torch.empty(self.hashgrid.max_blocks, 4, dtype=torch.int32, device=dev)
+        self.hashgrid.initialize(x, permutation, bin_offsets, block_info)
+        return HashGridSnapshot(grid=self.hashgrid, bin_offsets=bin_offsets, permutation=permutation,
+                                block_info=block_info, dim=self.dim)
+
+    def wrap_positions(self, x):
+        """Periodic: map each of the ``dim`` coordinates into ``[-L/2, L/2)``; clamped: identity."""
+        if self.boundary != "periodic":
+            return x
+        cols = []
+        for d in range(self.dim):
+            L = torch.tensor(self.grid_size[d] * self.eps, device=x.device)
+            cols.append(torch.remainder(x[..., d] + 0.5 * L, L) - 0.5 * L)
+        return torch.stack(cols, dim=-1)
+
+
+def _zeros_like_shape(shape, dtype, device):
+    return torch.zeros(shape, dtype=dtype, device=device)
+
+
+class Permute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, s, mass, snapshot):
+        x_bin, s_bin, mass_bin = torch.empty_like(x), torch.empty_like(s), torch.empty_like(mass)
+        snapshot.grid.bin_particles(x, s, mass, snapshot.permutation, x_bin, s_bin, mass_bin)
+        ctx.snapshot = snapshot
+        ctx.meta = (x.shape, s.shape, mass.shape, x.dtype, x.device)
+        ctx.needs = (x.requires_grad, s.requires_grad, mass.requires_grad)
+        return x_bin, s_bin, mass_bin
+
+    @staticmethod
+    def backward(ctx, g_x, g_s, g_m):
+        xs, ss, ms, dtype, device = ctx.meta
+        g_x = _zeros_like_shape(xs, dtype, device) if g_x is None else g_x.contiguous()
+        g_s = _zeros_like_shape(ss, dtype, device) if g_s is None else g_s.contiguous()
+        g_m = _zeros_like_shape(ms, dtype, device) if g_m is None else g_m.contiguous()
+        o_x, o_s, o_m = torch.empty_like(g_x), torch.empty_like(g_s), torch.empty_like(g_m)
+        snap = ctx.snapshot
+        snap.grid.backward_bin_particles(g_x, g_s, g_m, snap.permutation, o_x, o_s, o_m)
+        nx, ns, nm = ctx.needs
+        return (o_x if nx else None, o_s if ns else None, o_m if nm else None, None)
+
+
+def bin_particles(x, s, snapshot, mass=None):
+    no_mass = mass is None
+    out = Permute.apply(x, s, _default_mass(x, mass), snapshot)
+    return out[:2] if no_mass else out
+
+
+def unbin_particles(x_bin, s_bin, snapshot, mass_bin=None):
+    no_mass = mass_bin is None
+    mass_bin = _default_mass(x_bin, mass_bin)
+    x, s, mass = torch.empty_like(x_bin), torch.empty_like(s_bin), torch.empty_like(mass_bin)
+    snapshot.grid.backward_bin_particles(x_bin, s_bin, mass_bin, snapshot.permutation, x, s, mass)
+    return (x, s) if no_mass else (x, s, mass)
+
+
+class Count(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bin, snapshot):
+        out = torch.empty(x_bin.shape[:-1], dtype=torch.float32, device=x_bin.device)
+        snapshot.grid.count_forward(x_bin, out, snapshot.bin_offsets, snapshot.block_info)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        # a neighbour count is piecewise constant in the positions
+        return None, None
+
+
+def count(x_bin, snapshot):
+    return Count.apply(x_bin, snapshot)
+
+
+class Density(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bin, mass, snapshot):
+        rho = torch.empty(x_bin.shape[:-1], dtype=torch.float32, device=x_bin.device)
+        snapshot.grid.density_forward(x_bin, mass, rho, snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, mass)
+        ctx.snapshot = snapshot
+        ctx.dLdx = x_bin.requires_grad
+        return rho
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if not ctx.dLdx:
+            return None, None, None
+        x_bin, mass = ctx.saved_tensors
+        snap = ctx.snapshot
+        grad_x = torch.empty_like(x_bin)
+        snap.grid.density_backward(x_bin, mass, grad_output.contiguous(), grad_x, snap.bin_offsets,
+                                   snap.block_info, True)
+        return grad_x, None, None
+
+
+def density(x_bin, snapshot, mass=None):
+    return Density.apply(x_bin, _default_mass(x_bin, mass), snapshot)
+
+
+class _FeatureOp(torch.autograd.Function):
+    """Shared autograd plumbing of Blur and Gradient (inputs x_bin, s_bin, rho, mass, snapshot)."""
+
+    @staticmethod
+    def _forward(ctx, fwd_name, out_tail, x_bin, s_bin, rho, mass, snapshot):
+        out = torch.empty(*s_bin.shape, *out_tail, dtype=torch.float32, device=x_bin.device)
+        getattr(snapshot.grid, fwd_name)(x_bin, rho, mass, s_bin, out, snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, s_bin, rho, mass)
+        ctx.snapshot = snapshot
+        ctx.needs = (x_bin.requires_grad, s_bin.requires_grad, rho.requires_grad)
+        return out
+
+    @staticmethod
+    def _backward(ctx, bwd_name, grad_output):
+        x_bin, s_bin, rho, mass = ctx.saved_tensors
+        snap = ctx.snapshot
+        dLdx, dLds, dLdrho = ctx.needs
+        grad_x, grad_s, grad_rho = torch.empty_like(x_bin), torch.empty_like(s_bin), torch.empty_like(rho)
+        getattr(snap.grid, bwd_name)(x_bin, rho, mass, s_bin, grad_output.contiguous(), grad_x, grad_s, grad_rho,
+                                     snap.bin_offsets, snap.block_info, dLdx, dLds, dLdrho)
+        return (grad_x if dLdx else None, grad_s if dLds else None, grad_rho if dLdrho else None, None, None)
+
+
+class Blur(_FeatureOp):
+    @staticmethod
+    def forward(ctx, x_bin, s_bin, rho, mass, snapshot):
+        return _FeatureOp._forward(ctx, "blur_forward", (), x_bin, s_bin, rho, mass, snapshot)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _FeatureOp._backward(ctx, "blur_backward", grad_output)
+
+
+def blur(x_bin, rho, s_bin, snapshot, mass=None):
+    return Blur.apply(x_bin, s_bin, rho, _default_mass(x_bin, mass), snapshot)
+
+
+class Gradient(_FeatureOp):
+    @staticmethod
+    def forward(ctx, x_bin, s_bin, rho, mass, snapshot):
+        return _FeatureOp._forward(ctx, "gradient_forward", (snapshot.dim,), x_bin, s_bin, rho, mass, snapshot)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _FeatureOp._backward(ctx, "gradient_backward", grad_output)
+
+
+def gradient(x_bin, rho, s_bin, snapshot, mass=None):
+    return Gradient.apply(x_bin, s_bin, rho, _default_mass(x_bin, mass), snapshot)
+
+
+class DensityGradient(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bin, mass, snapshot):
+        out = torch.empty(*x_bin.shape[:-1], snapshot.dim, dtype=torch.float32, device=x_bin.device)
+        snapshot.grid.density_gradient_forward(x_bin, mass, out, snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, mass)
+        ctx.snapshot = snapshot
+        ctx.dLdx = x_bin.requires_grad
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if not ctx.dLdx:
+            return None, None, None
+        x_bin, mass = ctx.saved_tensors
+        snap = ctx.snapshot
+        grad_x = torch.empty_like(x_bin)
+        snap.grid.density_gradient_backward(x_bin, mass, grad_output.contiguous(), grad_x, snap.bin_offsets,
+                                            snap.block_info, True)
+        return grad_x, None, None
+
+
+def density_gradient(x_bin, snapshot, mass=None):
+    return DensityGradient.apply(x_bin, _default_mass(x_bin, mass), snapshot)
+
+
+class MomentMatrix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bin, rho, mass, snapshot):
+        dim = snapshot.dim
+        out = torch.empty(*x_bin.shape[:-1], dim, dim, dtype=torch.float32, device=x_bin.device)
+        snapshot.grid.moment_matrix_forward(x_bin, rho, mass, out, snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, rho, mass)
+        ctx.snapshot = snapshot
+        ctx.needs = (x_bin.requires_grad, rho.requires_grad)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_bin, rho, mass = ctx.saved_tensors
+        snap = ctx.snapshot
+        dLdx, dLdrho = ctx.needs
+        grad_x, grad_rho = torch.empty_like(x_bin), torch.empty_like(rho)
+        snap.grid.moment_matrix_backward(x_bin, rho, mass, grad_output.contiguous(), grad_x, grad_rho,
+                                         snap.bin_offsets, snap.block_info, dLdx, dLdrho)
+        return (grad_x if dLdx else None, grad_rho if dLdrho else None, None, None)
+
+
+def moment_matrix(x_bin, rho, snapshot, mass=None):
+    return MomentMatrix.apply(x_bin, rho, _default_mass(x_bin, mass), snapshot)
+
+
+@torch.no_grad()
+def safe_inv_sym_mat(M, rtol=1e-6):
+    M_inv = torch.empty_like(M)
+    sph_cuda.safe_inv_sym_mat(M, M_inv, rtol)
+    return M_inv
+
+
+def gradient_hybrid(x_bin, rho, s_bin, snapshot, mass=None):
+    """Moment-corrected gradient: value ``raw @ inv(M)``, gradient of the raw SPH gradient."""
+    with torch.no_grad():
+        M = moment_matrix(x_bin, rho, snapshot, mass=mass)
+        if snapshot.dim in (2, 3):
+            L = safe_inv_sym_mat(M, rtol=1e-3)
+        else:
+            L = torch.linalg.pinv(M, hermitian=True, rtol=1e-3)
+    raw = gradient(x_bin, rho, s_bin, snapshot, mass=mass)
+    return raw + (raw @ L - raw).detach()
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused perception step (extension; the reference issues one launch per operator).
+# ---------------------------------------------------------------------------------------------
+class Perception(torch.autograd.Function):
+    """rho = density(x); blur(x, rho, s); gradient(x, rho, s); density_gradient(x) as one node.
+
+    Forward runs two sweeps over the neighbour cells instead of four launches; backward runs the
+    chained two-sweep backward, or the features-only variant when ``x_bin`` needs no gradient.
+    """
+
+    @staticmethod
+    def forward(ctx, x_bin, s_bin, mass, snapshot, want_density_gradient):
+        B, N, C = s_bin.shape
+        dev, dim = x_bin.device, snapshot.dim
+        rho = torch.empty(B, N, dtype=torch.float32, device=dev)
+        s_blur = torch.empty_like(s_bin)
+        s_grad = torch.empty(B, N, C, dim, dtype=torch.float32, device=dev)
+        rho_grad = torch.empty(B, N, dim, dtype=torch.float32, device=dev) if want_density_gradient else None
+        snapshot.grid.perception_forward(x_bin, mass, s_bin, rho, None, rho_grad, s_blur, s_grad, None,
+                                         snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, s_bin, rho, *([] if mass is None else [mass]))
+        ctx.has_mass = mass is not None
+        ctx.snapshot = snapshot
+        ctx.needs = (x_bin.requires_grad, s_bin.requires_grad)
+        ctx.want_dg = want_density_gradient
+        if want_density_gradient:
+            return rho, s_blur, s_grad, rho_grad
+        return rho, s_blur, s_grad
+
+    @staticmethod
+    def backward(ctx, g_rho, g_blur, g_grad, g_rho_grad=None):
+        saved = ctx.saved_tensors
+        x_bin, s_bin, rho = saved[:3]
+        mass = saved[3] if ctx.has_mass else None
+        dLdx, dLds = ctx.needs
+        snap = ctx.snapshot
+        cont = lambda t: None if t is None else t.contiguous()
+        grad_x = torch.empty_like(x_bin) if dLdx else None
+        grad_s = torch.empty_like(s_bin) if dLds else None
+        scratch = torch.empty_like(rho) if dLdx else None
+        if dLdx or dLds:
+            snap.grid.perception_backward(x_bin, mass, s_bin, rho, cont(g_rho) if dLdx else None, cont(g_blur),
+                                          cont(g_grad), cont(g_rho_grad) if dLdx else None, grad_x, grad_s,
+                                          scratch, snap.bin_offsets, snap.block_info)
+        return grad_x, grad_s, None, None, None
+
+
+def perceive(x_bin, s_bin, snapshot, mass=None, with_density_gradient=True):
+    """Fused ``(rho, blur, gradient[, density_gradient])`` of binned particles.
+
+    Equivalent to ``rho = density(x_bin, snapshot, mass)``, ``blur(x_bin, rho, s_bin, ...)``,
+    ``gradient(x_bin, rho, s_bin, ...)`` and ``density_gradient(x_bin, ...)`` with gradients
+    flowing through ``rho`` into ``x_bin``.
+    """
+    if mass is not None:
+        mass = _default_mass(x_bin, mass)
+    return Perception.apply(x_bin, s_bin, mass, snapshot, with_density_gradient)

@@ -1,0 +1,142 @@
+"""The CUDA operators against the committed outputs of the reference's torch_sph.py."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden_names, load_golden
+from helpers import ATOL_SCALE, RTOL, np64
+from npa_b200.workloads import Workload
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(name):
+    """Bins the fixture's particles; returns everything in cell order plus the inverse map."""
+    from npa_b200 import sphops as sph
+    meta, arr = load_golden(name)
+    dim = meta["dim"]
+    x = torch.from_numpy(arr["in_x"])
+    B, N, _ = x.shape
+    if dim == 3:
+        x = torch.cat([x, torch.zeros(B, N, 1)], dim=-1)
+    w = Workload(name, dim=dim, B=B, N=N, C=meta["C"], eps=meta["eps"], grid_size=tuple(meta["grid"]),
+                 boundary="periodic" if meta["periodic"] else "clamped", max_particles_per_block=8)
+    grid = sph.HashGrid(dim=dim, boundary=w.boundary, mode="grid", grid_size=w.grid_size, eps=w.eps,
+                        num_particles=N, batch_size=B, max_particles_per_block=8)
+    snap = grid.instantiate(x.cuda())
+    perm = snap.permutation.long()
+
+    def binned(key, tail=()):
+        t = torch.from_numpy(arr[key]).cuda()
+        idx = perm.view(B, N, *([1] * len(tail))).expand(B, N, *tail)
+        return torch.empty_like(t).scatter_(1, idx, t).contiguous()
+
+    return sph, meta, arr, snap, perm, binned, x.cuda()
+
+
+def _unbin(t, perm):
+    idx = perm.view(*perm.shape, *([1] * (t.dim() - 2))).expand_as(t)
+    return torch.gather(t, 1, idx)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_forward_against_reference_outputs(name):
+    sph, meta, arr, snap, perm, binned, x = _setup(name)
+    dim, C = meta["dim"], meta["C"]
+    s = torch.from_numpy(arr["in_s"]).cuda()
+    mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
+    if mass is None:
+        xb, sb = sph.bin_particles(x, s, snap)
+        mb = None
+    else:
+        xb, sb, mb = sph.bin_particles(x, s, snap, mass)
+    rho_in = binned("in_rho_in")
+    got = {
+        "count": sph.count(xb, snap),
+        "rho": sph.density(xb, snap, mb),
+        "rho_grad": sph.density_gradient(xb, snap, mb),
+        "blur": sph.blur(xb, rho_in, sb, snap, mb),
+        "grad": sph.gradient(xb, rho_in, sb, snap, mb),
+        "moment": sph.moment_matrix(xb, rho_in, snap, mb),
+    }
+    np.testing.assert_array_equal(_unbin(got["count"], perm).cpu().numpy(), arr["f32_count"])
+    for k in ("rho", "rho_grad", "blur", "grad", "moment"):
+        out = np64(_unbin(got[k], perm))
+        assert_close(out, arr[f"f64_{k}"], RTOL, ATOL_SCALE, what=f"{name}:{k} vs fp64 reference")
+        # the reference's own fp32 run is itself only fp32-accurate: a looser cross-check
+        assert_close(out, arr[f"f32_{k}"], 1e-4, 4e-6, what=f"{name}:{k} vs fp32 reference")
+    # the fused forward gives the same tensors as the single operators
+    rho_f, blur_f, grad_f, dg_f = sph.perceive(xb, sb, snap, mb)
+    assert torch.equal(rho_f, got["rho"]) and torch.equal(dg_f, got["rho_grad"])
+    assert torch.equal(blur_f, sph.blur(xb, rho_f, sb, snap, mb))
+    assert torch.equal(grad_f, sph.gradient(xb, rho_f, sb, snap, mb))
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_backward_against_reference_autograd(name):
+    sph, meta, arr, snap, perm, binned, x = _setup(name)
+    dim, C = meta["dim"], meta["C"]
+    s = torch.from_numpy(arr["in_s"]).cuda()
+    mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
+    if mass is None:
+        xb, sb = sph.bin_particles(x, s, snap)
+        mb = None
+    else:
+        xb, sb, mb = sph.bin_particles(x, s, snap, mass)
+    rho_in = binned("in_rho_in")
+    ups = {"g_rho": binned("in_g_rho"), "g_rho_grad": binned("in_g_rho_grad", (dim,)),
+           "g_blur": binned("in_g_blur", (C,)), "g_grad": binned("in_g_grad", (C, dim)),
+           "g_moment": binned("in_g_moment", (dim, dim))}
+
+    def run(fn, up):
+        xr = xb.clone().requires_grad_(True)
+        sr = sb.clone().requires_grad_(True)
+        rr = rho_in.clone().requires_grad_(True)
+        fn(xr, sr, rr).backward(up)
+        return xr.grad, sr.grad, rr.grad
+
+    ops = {
+        "density": (lambda xr, sr, rr: sph.density(xr, snap, mb), "g_rho"),
+        "rho_grad": (lambda xr, sr, rr: sph.density_gradient(xr, snap, mb), "g_rho_grad"),
+        "blur": (lambda xr, sr, rr: sph.blur(xr, rr, sr, snap, mb), "g_blur"),
+        "grad": (lambda xr, sr, rr: sph.gradient(xr, rr, sr, snap, mb), "g_grad"),
+        "moment": (lambda xr, sr, rr: sph.moment_matrix(xr, rr, snap, mb), "g_moment"),
+    }
+    for op, (fn, up) in ops.items():
+        dx, ds, dr = run(fn, ups[up])
+        assert_close(np64(_unbin(dx, perm))[..., :dim], arr[f"f64_bw_{op}_dx"], RTOL, ATOL_SCALE, f"{name}:{op} dx")
+        if dim == 3:
+            assert float(dx[..., 3].abs().max()) == 0.0
+        if f"f64_bw_{op}_ds" in arr:
+            assert_close(np64(_unbin(ds, perm)), arr[f"f64_bw_{op}_ds"], RTOL, ATOL_SCALE, f"{name}:{op} ds")
+        if f"f64_bw_{op}_drho" in arr:
+            assert_close(np64(_unbin(dr, perm)), arr[f"f64_bw_{op}_drho"], RTOL, ATOL_SCALE, f"{name}:{op} drho")
+
+
+@pytest.mark.parametrize("name", golden_names())
+@pytest.mark.parametrize("fused", [False, True], ids=["per_op", "fused"])
+def test_chained_backward_against_reference_autograd(name, fused):
+    sph, meta, arr, snap, perm, binned, x = _setup(name)
+    dim, C = meta["dim"], meta["C"]
+    s = torch.from_numpy(arr["in_s"]).cuda()
+    mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
+    xr = x.clone().requires_grad_(True)
+    sr = s.clone().requires_grad_(True)
+    if mass is None:
+        xb, sb = sph.bin_particles(xr, sr, snap)
+        mb = None
+    else:
+        xb, sb, mb = sph.bin_particles(xr, sr, snap, mass)
+    if fused:
+        rho, blur, grad, dg = sph.perceive(xb, sb, snap, mb)
+    else:
+        rho = sph.density(xb, snap, mb)
+        blur = sph.blur(xb, rho, sb, snap, mb)
+        grad = sph.gradient(xb, rho, sb, snap, mb)
+        dg = sph.density_gradient(xb, snap, mb)
+    torch.autograd.backward([rho, blur, grad, dg],
+                            [binned("in_g_rho"), binned("in_g_blur", (C,)), binned("in_g_grad", (C, dim)),
+                             binned("in_g_rho_grad", (dim,))])
+    # gradients arrive in the original particle order through Permute.backward
+    assert_close(np64(xr.grad)[..., :dim], arr["f64_chain_dx"], RTOL, ATOL_SCALE, f"{name}: chain dx")
+    assert_close(np64(sr.grad), arr["f64_chain_ds"], RTOL, ATOL_SCALE, f"{name}: chain ds")
