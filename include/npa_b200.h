@@ -205,6 +205,38 @@ int npa_moment_matrix_backward(const npa_grid *g, const float *x_bin,
 int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
                          float tol, void *stream);
 
+/* ---- blur + gradient in one launch ------------------------------------------ *
+ * The two feature operators share every pair test and every neighbour feature
+ * load, so one sweep produces both.  Results equal npa_blur_* / npa_gradient_*
+ * (sph_cuda.cu:2191-2365 forward, :2580-2728 and :2810-2958 backward); either
+ * output (forward) or upstream gradient (backward) may be NULL.               */
+int npa_blur_gradient_forward(const npa_grid *g, int32_t channels, const float *x_bin,
+                              const float *rho, const float *mass, const float *s_bin,
+                              float *s_blur, float *s_grad, const int32_t *bin_offsets,
+                              const int32_t *block_info, void *stream);
+
+/* grad_x == NULL and grad_rho == NULL selects the variant that differentiates
+ * with respect to s only. */
+int npa_blur_gradient_backward(const npa_grid *g, int32_t channels, const float *x_bin,
+                               const float *rho, const float *mass, const float *s_bin,
+                               const float *dL_dblur, const float *dL_dgrad, float *grad_x,
+                               float *grad_s, float *grad_rho, const int32_t *bin_offsets,
+                               const int32_t *block_info, void *stream);
+
+/* ---- density + density gradient backward in one launch ---------------------- *
+ * Gradient with respect to the positions of  rho = density(x)  and
+ * density_gradient(x)  in one sweep (sph_cuda.cu:2501-2578 and :2730-2808 as two
+ * launches in the reference).  The upstream gradient of rho is the sum of
+ * dL_drho_a and dL_drho_b (either may be NULL), which is how the gradient that
+ * blur / gradient return for their rho input joins the one given for rho
+ * itself; dL_drho_grad may be NULL.  With accumulate != 0 the result is added
+ * to grad_x instead of overwriting it.                                        */
+int npa_density_chain_backward(const npa_grid *g, const float *x_bin, const float *mass,
+                               const float *dL_drho_a, const float *dL_drho_b,
+                               const float *dL_drho_grad, float *grad_x, int32_t accumulate,
+                               const int32_t *bin_offsets, const int32_t *block_info,
+                               void *stream);
+
 /* ---- fused perception (one launch set for what NPA.perceive asks for) ---- *
  * The reference runs density, blur, gradient, density_gradient and
  * moment_matrix as separate launches that each re-stage the same neighbour

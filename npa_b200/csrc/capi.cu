@@ -208,6 +208,55 @@ int npa_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_b
     return launch_feature_backward(g, F_GRAD, grad_x || grad_rho, a, (cudaStream_t)stream);
 }
 
+int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                              const float *mass, const float *s_bin, float *s_blur, float *s_grad,
+                              const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("blur_gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("blur_gradient_forward", channels)) != NPA_OK) return rc;
+    NPA_REQUIRE(rho, "blur_gradient_forward", "rho");
+    NPA_REQUIRE(s_bin, "blur_gradient_forward", "state_in");
+    const int mask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
+    if (!mask) return NPA_OK;
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info};
+    return launch_feature_forward(g, mask, a, (cudaStream_t)stream);
+}
+
+int npa_blur_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
+                               const float *mass, const float *s_bin, const float *dL_dblur,
+                               const float *dL_dgrad, float *grad_x, float *grad_s, float *grad_rho,
+                               const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+    Geom g;
+    int rc = begin_op("blur_gradient_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    if ((rc = check_channels("blur_gradient_backward", channels)) != NPA_OK) return rc;
+    if (!grad_x && !grad_s && !grad_rho) return NPA_OK;
+    NPA_REQUIRE(rho, "blur_gradient_backward", "rho");
+    NPA_REQUIRE(s_bin, "blur_gradient_backward", "state_in");
+    if ((rc = check_grad_x("blur_gradient_backward", g, grad_x)) != NPA_OK) return rc;
+    const int mask = (dL_dblur ? F_BLUR : 0) | (dL_dgrad ? F_GRAD : 0);
+    if (!mask) return fail(NPA_ERR_INVALID_ARGUMENT, "blur_gradient_backward: both upstream gradients are NULL");
+    FeatureBwdArgs a = {x_bin, mass, rho, s_bin, dL_dblur, dL_dgrad, grad_x, grad_s, grad_rho, channels, bin_offsets, block_info};
+    return launch_feature_backward(g, mask, grad_x || grad_rho, a, (cudaStream_t)stream);
+}
+
+int npa_density_chain_backward(const npa_grid *gd, const float *x_bin, const float *mass, const float *dL_drho_a,
+                               const float *dL_drho_b, const float *dL_drho_grad, float *grad_x,
+                               int32_t accumulate, const int32_t *bin_offsets, const int32_t *block_info,
+                               void *stream) {
+    Geom g;
+    int rc = begin_op("density_chain_backward", gd, &g, x_bin, bin_offsets, block_info);
+    if (rc != NPA_OK) return rc;
+    NPA_REQUIRE(grad_x, "density_chain_backward", "grad_x");
+    if ((rc = check_grad_x("density_chain_backward", g, grad_x)) != NPA_OK) return rc;
+    const int mask = ((dL_drho_a || dL_drho_b) ? S_DENSITY : 0) | (dL_drho_grad ? S_DGRAD : 0);
+    if (!mask) return fail(NPA_ERR_INVALID_ARGUMENT, "density_chain_backward: every upstream gradient is NULL");
+    ScalarBwdArgs a = {x_bin, mass, nullptr, dL_drho_a, dL_drho_b, dL_drho_grad, nullptr, grad_x, nullptr,
+                       accumulate ? 1 : 0, bin_offsets, block_info};
+    return launch_scalar_backward(g, mask, a, (cudaStream_t)stream);
+}
+
 int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *mass,
                            const float *s_bin, float *rho, float *count, float *rho_grad, float *s_blur,
                            float *s_grad, float *moment, const int32_t *bin_offsets,

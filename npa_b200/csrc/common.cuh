@@ -27,8 +27,10 @@ struct Geom {
     float inv_eps;  // 1.0f / float(eps): the multiplier pos2cell uses
     float h;        // float(eps)
     float h2;       // float(eps * eps) rounded once from double, as torch does
-    float L[3];     // box length per axis = g * eps
+    float L[3];     // box length per axis = g * eps (rounded from double)
+    float Llo[3];   // double(g * eps) - L: the part of the box length fp32 cannot hold
     float invL[3];
+    float halfL[3];
     float c_s;      // poly6 normalisation
     float c_g;      // spiky normalisation
 };
@@ -126,9 +128,13 @@ __device__ inline int axis_cell(float x, const Geom &g, int axis) {
 
 // ---- pair geometry -----------------------------------------------------------
 
-// Minimum-image displacement component for a periodic axis.
-__device__ inline float min_image(float d, float L, float invL) {
-    return __fmaf_rn(-L, rintf(d * invL), d);
+// General minimum image of one displacement component: used only when the
+// image shift could not be known in advance (a particle outside the primary
+// box, or an axis with fewer than three cells).
+__device__ inline float wrap_general(float r, float L, float Llo, float invL) {
+    const float n = rintf(r * invL);
+    r = __fmaf_rn(-n, L, r);
+    return __fmaf_rn(-n, Llo, r);
 }
 
 // r^2 accumulated in the order torch.sum uses on a length-D vector, without

@@ -65,7 +65,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     constexpr int PPW = 32 / LPP;
     constexpr int CAP = kListPerWarp / PPW;
     constexpr unsigned SUBMASK = LPP == 32 ? 0xffffffffu : ((1u << LPP) - 1u);
-    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     __shared__ float4 s_ent[kWarpsPerCta][kListPerWarp];
     __shared__ int s_idx[kWarpsPerCta][kListPerWarp];
 
@@ -74,7 +74,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     if (row >= g.max_blocks) return;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) return;
-    int2 *rng = s_ranges[warp];
+    int4 *rng = s_ranges[warp];
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
     const int sub = lane / LPP, sl = lane % LPP;
     float4 *ent = s_ent[warp] + sub * CAP;
@@ -123,14 +123,15 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             };
 
             for (int r = 0; r < nr; ++r) {
-                const int2 rg = rng[r];
+                const int4 rg = rng[r];
+                const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
                 for (int j0 = rg.x; j0 < rg.y; j0 += LPP) {
                     const int j = j0 + sl;
                     float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
                     bool acc = false;
                     if (ivalid && j < rg.y) {
                         const Pos<D> pj = load_pos<D>(a.x, j);
-                        q = displacement<D, PER>(g, pi, pj, rx, ry, rz);
+                        q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
                         acc = q < g.h2;
                     }
                     const unsigned bal = __ballot_sync(kFull, acc);
@@ -179,7 +180,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
     constexpr int PPW = 32 / LPP;
     constexpr int CAP = kListPerWarp / PPW;
     constexpr unsigned SUBMASK = LPP == 32 ? 0xffffffffu : ((1u << LPP) - 1u);
-    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z v_j
     __shared__ float4 s_ker[kWarpsPerCta][kListPerWarp];  // W, 6(h^2-q)^2, phi, psi
     __shared__ int s_idx[kWarpsPerCta][kListPerWarp];
@@ -189,7 +190,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
     if (row >= g.max_blocks) return;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) return;
-    int2 *rng = s_ranges[warp];
+    int4 *rng = s_ranges[warp];
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
     const int sub = lane / LPP, sl = lane % LPP;
     float4 *geo = s_geo[warp] + sub * CAP;
@@ -291,14 +292,15 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             };
 
             for (int r = 0; r < nr; ++r) {
-                const int2 rg = rng[r];
+                const int4 rg = rng[r];
+                const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
                 for (int j0 = rg.x; j0 < rg.y; j0 += LPP) {
                     const int j = j0 + sl;
                     float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
                     bool acc = false;
                     if (ivalid && j < rg.y) {
                         const Pos<D> pj = load_pos<D>(a.x, j);
-                        q = displacement<D, PER>(g, pi, pj, rx, ry, rz);
+                        q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
                         acc = q < g.h2;
                     }
                     const unsigned bal = __ballot_sync(kFull, acc);

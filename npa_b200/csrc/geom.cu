@@ -96,8 +96,11 @@ int make_geom(const npa_grid *in, Geom *out) {
     g.inv_eps = 1.0f / eps_f;
     g.h2 = (float)(in->eps * in->eps);
     for (int d = 0; d < 3; ++d) {
-        g.L[d] = (float)g.g[d] * eps_f;
+        const double Ld = (double)g.g[d] * in->eps;
+        g.L[d] = (float)Ld;
+        g.Llo[d] = (float)(Ld - (double)g.L[d]);
         g.invL[d] = 1.0f / g.L[d];
+        g.halfL[d] = 0.5f * g.L[d];
     }
     const double pi = 3.14159265358979323846;
     if (in->dim == 2) {

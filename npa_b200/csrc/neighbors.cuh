@@ -35,8 +35,13 @@ __device__ inline WorkItem load_item(const int32_t *__restrict__ block_info,
 }
 
 // Neighbour coordinate along one axis; false when the clamped grid ends there
-// or when a small periodic axis would visit the same cell twice.
-__device__ inline bool neighbor_axis(int c, int o, int n, int periodic, int &out) {
+// or when a small periodic axis would visit the same cell twice.  `shift` is
+// the periodic image the neighbour cell lies in relative to cell c: -1 when the
+// walk left the grid below 0 (its particles sit one box length higher, so the
+// displacement needs -L), +1 above, 0 otherwise or when the axis is too short
+// to tell (then the half-box test in periodic_delta decides per pair).
+__device__ inline bool neighbor_axis(int c, int o, int n, int periodic, int &out, int &shift) {
+    shift = 0;
     if (!periodic) {
         out = c + o;
         return out >= 0 && out < n;
@@ -50,8 +55,48 @@ __device__ inline bool neighbor_axis(int c, int o, int n, int periodic, int &out
         return o >= 0;
     }
     out = c + o;
-    out = out < 0 ? out + n : (out >= n ? out - n : out);
+    if (out < 0) { out += n; shift = -1; }
+    else if (out >= n) { out -= n; shift = 1; }
     return true;
+}
+
+// Candidate range [x, y) of global particle indices plus the image shift code
+// (sx+1) | (sy+1) << 2 | (sz+1) << 4 in z.
+__device__ inline int shift_code(int sx, int sy, int sz) { return (sx + 1) | ((sy + 1) << 2) | ((sz + 1) << 4); }
+
+// Position of particle i as seen from one candidate range.  For a periodic grid
+// the range carries the image shift S = k * L (k in {-1, 0, 1} per axis) of the
+// neighbour cell, and the displacement is r = x_j - x_i + S.  Evaluating
+// (x_j + S) - x_i in fp32 would round at the magnitude of the box; instead the
+// shifted origin x_i - S is formed once per (particle, range) as an unevaluated
+// sum  x + e  (error-free two-sum, with S itself split in a high and a low fp32
+// part because g * eps is not representable), so that per pair
+// r = (x_j - x) + c  with c = S_lo - e is as accurate as a clamped displacement.
+template <int D, bool PER>
+struct Origin {
+    float x[3];
+    float c[3];
+};
+
+template <int D, bool PER>
+__device__ inline Origin<D, PER> make_origin(const Geom &g, float px, float py, float pz, int code) {
+    Origin<D, PER> o;
+    const float p[3] = {px, py, pz};
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+        o.x[d] = p[d];
+        o.c[d] = 0.f;
+        if (PER && d < D) {
+            const float k = (float)(((code >> (2 * d)) & 3) - 1);
+            const float b = -k * g.L[d];
+            const float sum = __fadd_rn(p[d], b);
+            const float bb = __fsub_rn(sum, p[d]);
+            const float err = __fadd_rn(__fsub_rn(p[d], __fsub_rn(sum, bb)), __fsub_rn(b, bb));
+            o.x[d] = sum;
+            o.c[d] = __fsub_rn(k * g.Llo[d], err);
+        }
+    }
+    return o;
 }
 
 // Fills rng[0..n) with the non-empty candidate ranges [start, end) of global
@@ -59,18 +104,18 @@ __device__ inline bool neighbor_axis(int c, int o, int n, int periodic, int &out
 // lanes; rng is per-warp shared memory of kMaxRanges entries.
 template <int D>
 __device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bin_offsets,
-                                   const WorkItem &it, int2 *rng) {
+                                   const WorkItem &it, int4 *rng) {
     const int lane = threadIdx.x & 31;
     int cx, cy, cz;
     hash_to_cell<D>(g, (uint32_t)(it.cell - it.sys * g.cells), cx, cy, cz);
     const int32_t *off = bin_offsets + (size_t)it.sys * g.cells;
-    int start = 0, end = 0;
+    int start = 0, end = 0, sx = 0, sy = 0, sz = 0;
     if (!g.morton) {
         const int row = lane >> 1, piece = lane & 1;
         if (row < (D == 2 ? 3 : 9)) {
             int ny = 0, nz = 0;
-            bool ok = neighbor_axis(cy, row % 3 - 1, g.g[1], g.periodic, ny);
-            if (D == 3) ok = neighbor_axis(cz, row / 3 - 1, g.g[2], g.periodic, nz) && ok;
+            bool ok = neighbor_axis(cy, row % 3 - 1, g.g[1], g.periodic, ny, sy);
+            if (D == 3) ok = neighbor_axis(cz, row / 3 - 1, g.g[2], g.periodic, nz, sz) && ok;
             const int gx = g.g[0];
             int xlo = 0, xhi = -1;
             if (!g.periodic) {
@@ -78,9 +123,9 @@ __device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bi
             } else if (gx <= 3) {
                 if (piece == 0) { xlo = 0; xhi = gx - 1; }
             } else if (cx == 0) {
-                if (piece == 0) { xlo = 0; xhi = 1; } else { xlo = xhi = gx - 1; }
+                if (piece == 0) { xlo = 0; xhi = 1; } else { xlo = xhi = gx - 1; sx = -1; }
             } else if (cx == gx - 1) {
-                if (piece == 0) { xlo = gx - 2; xhi = gx - 1; } else { xlo = xhi = 0; }
+                if (piece == 0) { xlo = gx - 2; xhi = gx - 1; } else { xlo = xhi = 0; sx = 1; }
             } else if (piece == 0) {
                 xlo = cx - 1; xhi = cx + 1;
             }
@@ -92,9 +137,9 @@ __device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bi
     } else {
         if (lane < (D == 2 ? 9 : 27)) {
             int nx = 0, ny = 0, nz = 0;
-            bool ok = neighbor_axis(cx, lane % 3 - 1, g.g[0], g.periodic, nx);
-            ok = neighbor_axis(cy, (lane / 3) % 3 - 1, g.g[1], g.periodic, ny) && ok;
-            if (D == 3) ok = neighbor_axis(cz, lane / 9 - 1, g.g[2], g.periodic, nz) && ok;
+            bool ok = neighbor_axis(cx, lane % 3 - 1, g.g[0], g.periodic, nx, sx);
+            ok = neighbor_axis(cy, (lane / 3) % 3 - 1, g.g[1], g.periodic, ny, sy) && ok;
+            if (D == 3) ok = neighbor_axis(cz, lane / 9 - 1, g.g[2], g.periodic, nz, sz) && ok;
             if (ok) {
                 const uint32_t hsh = cell_hash<D>(g, nx, ny, nz);
                 start = __ldg(off + hsh);
@@ -104,7 +149,7 @@ __device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bi
     }
     const bool nonempty = end > start;
     const unsigned m = __ballot_sync(kFull, nonempty);
-    if (nonempty) rng[__popc(m & ((1u << lane) - 1))] = make_int2(start, end);
+    if (nonempty) rng[__popc(m & ((1u << lane) - 1))] = make_int4(start, end, shift_code(sx, sy, sz), 0);
     __syncwarp();
     return __popc(m);
 }
@@ -129,14 +174,18 @@ __device__ inline Pos<D> load_pos(const float *__restrict__ x, long long idx) {
 
 // r = x_j - x_i (minimum image when PER) and q = |r|^2.
 template <int D, bool PER>
-__device__ inline float displacement(const Geom &g, const Pos<D> &pi, const Pos<D> &pj, float &rx, float &ry, float &rz) {
-    rx = pj.x - pi.x;
-    ry = pj.y - pi.y;
-    rz = D == 3 ? pj.z - pi.z : 0.f;
+__device__ inline float displacement(const Geom &g, const Origin<D, PER> &o, float jx, float jy, float jz,
+                                     float &rx, float &ry, float &rz) {
+    rx = jx - o.x[0];
+    ry = jy - o.x[1];
+    rz = D == 3 ? jz - o.x[2] : 0.f;
     if (PER) {
-        rx = min_image(rx, g.L[0], g.invL[0]);
-        ry = min_image(ry, g.L[1], g.invL[1]);
-        if (D == 3) rz = min_image(rz, g.L[2], g.invL[2]);
+        rx += o.c[0];
+        ry += o.c[1];
+        if (D == 3) rz += o.c[2];
+        if (fabsf(rx) > g.halfL[0]) rx = wrap_general(rx, g.L[0], g.Llo[0], g.invL[0]);
+        if (fabsf(ry) > g.halfL[1]) ry = wrap_general(ry, g.L[1], g.Llo[1], g.invL[1]);
+        if (D == 3 && fabsf(rz) > g.halfL[2]) rz = wrap_general(rz, g.L[2], g.Llo[2], g.invL[2]);
     }
     return sq_norm<D>(rx, ry, rz);
 }

@@ -18,13 +18,13 @@ constexpr int kScalarPpw = 32 / kScalarLpp;    // particles per warp pass
 template <int D, bool PER, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
-    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + warp;
     if (row >= g.max_blocks) return;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) return;
-    int2 *rng = s_ranges[warp];
+    int4 *rng = s_ranges[warp];
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
     const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
     constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
@@ -38,13 +38,14 @@ scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
         const Pos<D> pi = load_pos<D>(a.x, i);
         float cnt = 0.f, rho = 0.f, dg[3] = {0.f, 0.f, 0.f}, mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int r = 0; r < nr; ++r) {
-            const int2 rg = rng[r];
+            const int4 rg = rng[r];
+            const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
             for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
                 const int j = j0 + sl;
                 if (!(ivalid && j < rg.y)) continue;
                 const Pos<D> pj = load_pos<D>(a.x, j);
                 float rx, ry, rz;
-                const float q = displacement<D, PER>(g, pi, pj, rx, ry, rz);
+                const float q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
                 if (!(q < g.h2)) continue;
                 if (MASK & S_COUNT) cnt += 1.0f;
                 const float mj = (kPoly || kSpiky) ? (a.mass ? __ldg(a.mass + j) : 1.0f) : 0.f;
@@ -123,13 +124,13 @@ __device__ inline void apply_jacobian(float phi, float psi, float rx, float ry, 
 template <int D, bool PER, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
-    __shared__ int2 s_ranges[kWarpsPerCta][kMaxRanges];
+    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarpsPerCta + warp;
     if (row >= g.max_blocks) return;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) return;
-    int2 *rng = s_ranges[warp];
+    int4 *rng = s_ranges[warp];
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
     const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
     constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
@@ -158,13 +159,14 @@ scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
         float dxg[3] = {0.f, 0.f, 0.f};  // spiky part, scaled by c_g at the end
         float drho = 0.f;
         for (int r = 0; r < nr; ++r) {
-            const int2 rg = rng[r];
+            const int4 rg = rng[r];
+            const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
             for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
                 const long long j = j0 + sl;
                 if (!(ivalid && j < rg.y)) continue;
                 const Pos<D> pj = load_pos<D>(a.x, j);
                 float rv[3];
-                const float q = displacement<D, PER>(g, pi, pj, rv[0], rv[1], rv[2]);
+                const float q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rv[0], rv[1], rv[2]);
                 if (!(q < g.h2) || !(q > 0.f)) continue;  // the self / coincident pair has zero gradient
                 const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                 if (MASK & S_DENSITY) {

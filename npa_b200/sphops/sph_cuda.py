@@ -130,11 +130,12 @@ class _HashGridBase:
         C = sin.shape[2] if isinstance(sin, torch.Tensor) and sin.dim() == 3 else -1
         self._pos(xin, names[0])
         self._bn(sin, names[1], C)
-        self._bn(min_, names[2])
         _check(permutation, (self._B, self._N), "permutation", torch.int32)
         self._pos(xout, names[3])
         self._bn(sout, names[4], C)
-        self._bn(mout, names[5])
+        if min_ is not None or mout is not None:  # extension: mass may be left out altogether
+            self._bn(min_, names[2])
+            self._bn(mout, names[5])
         if C == 0:
             sin = sout = None
         self._call(fn, xin, self._ref(), C, N.ptr(xin), N.ptr(sin), N.ptr(min_), N.ptr(permutation),
@@ -284,6 +285,71 @@ class _HashGridBase:
         self._call(_lib.npa_moment_matrix_backward, binned_positions, self._ref(), N.ptr(binned_positions),
                    N.ptr(rho), N.ptr(mass), N.ptr(dL_moment_matrix_out), N.ptr(grad_x if dLdx else None),
                    N.ptr(grad_rho if dLdrho else None), N.ptr(bin_offsets), N.ptr(block_info))
+
+    # ---- fused sweeps (no counterpart in the reference module) ------------------
+    def blur_gradient_forward(self, binned_positions, rho, mass, state_in, state_out, state_gradient_out,
+                              bin_offsets, block_info):
+        """blur and gradient in one launch; ``mass`` and either output may be None."""
+        C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
+        self._pos(binned_positions, "binned_positions")
+        self._bn(rho, "rho")
+        self._bn(state_in, "state_in", C)
+        if mass is not None:
+            self._bn(mass, "mass")
+        if state_out is not None:
+            self._bn(state_out, "state_out", C)
+        if state_gradient_out is not None:
+            self._bn(state_gradient_out, "state_gradient_out", C, self._dim)
+        self._snap(bin_offsets, block_info)
+        if C == 0:
+            return
+        self._call(_lib.npa_blur_gradient_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
+                   N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(state_out), N.ptr(state_gradient_out),
+                   N.ptr(bin_offsets), N.ptr(block_info))
+
+    def blur_gradient_backward(self, binned_positions, rho, mass, state_in, dL_blur_state_out, dL_grad_state_out,
+                               grad_x, grad_s, grad_rho, bin_offsets, block_info):
+        """Backward of both feature operators in one launch; None outputs are not computed."""
+        C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
+        self._pos(binned_positions, "binned_positions")
+        self._bn(rho, "rho")
+        self._bn(state_in, "state_in", C)
+        if mass is not None:
+            self._bn(mass, "mass")
+        if dL_blur_state_out is not None:
+            self._bn(dL_blur_state_out, "dL_blur_state_out", C)
+        if dL_grad_state_out is not None:
+            self._bn(dL_grad_state_out, "dL_grad_state_out", C, self._dim)
+        if grad_x is not None:
+            self._pos(grad_x, "grad_x")
+        if grad_s is not None:
+            self._bn(grad_s, "grad_s", C)
+        if grad_rho is not None:
+            self._bn(grad_rho, "grad_rho")
+        self._snap(bin_offsets, block_info)
+        if C == 0:
+            return
+        self._call(_lib.npa_blur_gradient_backward, binned_positions, self._ref(), C, N.ptr(binned_positions),
+                   N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(dL_blur_state_out), N.ptr(dL_grad_state_out),
+                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(grad_rho), N.ptr(bin_offsets), N.ptr(block_info))
+
+    def density_chain_backward(self, binned_positions, mass, dL_rho_a, dL_rho_b, dL_density_gradient_out, grad_x,
+                               accumulate, bin_offsets, block_info):
+        """density (+ density gradient) backward; the two rho upstreams are summed."""
+        self._pos(binned_positions, "binned_positions")
+        if mass is not None:
+            self._bn(mass, "mass")
+        if dL_rho_a is not None:
+            self._bn(dL_rho_a, "dL_rho_a")
+        if dL_rho_b is not None:
+            self._bn(dL_rho_b, "dL_rho_b")
+        if dL_density_gradient_out is not None:
+            self._bn(dL_density_gradient_out, "dL_density_gradient_out", self._dim)
+        self._pos(grad_x, "grad_x")
+        self._snap(bin_offsets, block_info)
+        self._call(_lib.npa_density_chain_backward, binned_positions, self._ref(), N.ptr(binned_positions),
+                   N.ptr(mass), N.ptr(dL_rho_a), N.ptr(dL_rho_b), N.ptr(dL_density_gradient_out), N.ptr(grad_x),
+                   1 if accumulate else 0, N.ptr(bin_offsets), N.ptr(block_info))
 
     # ---- fused perception (no counterpart in the reference module) -------------
     def perception_forward(self, binned_positions, mass, state_in, rho, count, density_gradient_out,

@@ -25,7 +25,7 @@ HERE = Path(__file__).resolve().parent
 CASES = {
     # name: dim, B, N, C, eps, grid, periodic, with_mass, position sampler
     "d2_clamped_mass": dict(dim=2, B=2, N=192, C=8, eps=0.1, grid=(16, 16), periodic=False, mass=True, spread="rand", scale=0.4),
-    "d2_periodic": dict(dim=2, B=2, N=160, C=6, eps=0.15, grid=(8, 6), periodic=True, mass=False, spread="randn", scale=0.5),
+    "d2_periodic": dict(dim=2, B=2, N=160, C=6, eps=0.15, grid=(8, 6), periodic=True, mass=False, spread="randn", scale=0.3),
     "d3_clamped": dict(dim=3, B=1, N=256, C=4, eps=0.4, grid=(6, 6, 6), periodic=False, mass=False, spread="rand", scale=1.0),
     "d3_periodic_mass": dict(dim=3, B=2, N=200, C=5, eps=0.3, grid=(6, 5, 4), periodic=True, mass=True, spread="randn", scale=0.6),
 }

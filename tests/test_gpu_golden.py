@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from conftest import assert_close, golden_names, load_golden
-from helpers import ATOL_SCALE, RTOL, np64
+from helpers import np64, tolerance
 from npa_b200.workloads import Workload
 
 pytestmark = pytest.mark.gpu
@@ -43,6 +43,7 @@ def _unbin(t, perm):
 def test_forward_against_reference_outputs(name):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
+    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     if mass is None:
@@ -76,6 +77,7 @@ def test_forward_against_reference_outputs(name):
 def test_backward_against_reference_autograd(name):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
+    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     if mass is None:
@@ -118,6 +120,7 @@ def test_backward_against_reference_autograd(name):
 def test_chained_backward_against_reference_autograd(name, fused):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
+    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     xr = x.clone().requires_grad_(True)
