@@ -99,6 +99,33 @@ int npa_grid_build(const npa_grid *g, const float *x, int32_t *permutation,
                    int64_t scratch_bytes, void *stream);
 
 /*
+ * Same binning as npa_grid_build(), for callers that cannot hand over scratch memory.
+ * (No counterpart in the reference: its grid object cudaMallocs its work arrays.)
+ *
+ * Who needs this: a host program that owns all device memory itself -- a simulation or
+ * inference server that partitions the GPU into fixed arenas at start-up, or a plugin host
+ * that only passes in the buffers it registered -- and therefore forbids its plugins to call
+ * cudaMalloc (an allocation there can fail late, fragments the arena, and synchronises the
+ * whole device in the middle of a step).  Such a caller still passes x and the three outputs,
+ * but has nowhere to take the work arrays from.
+ *
+ * The work arrays live in one fixed array inside the library (device global memory,
+ * NPA_STATIC_SCRATCH_BYTES, reserved on every GPU that loads the library until the process
+ * exits).  Consequences:
+ *   - geometries with npa_grid_scratch_bytes(g) > NPA_STATIC_SCRATCH_BYTES are refused with
+ *     NPA_ERR_SCRATCH_TOO_SMALL and nothing is launched;
+ *   - the first call on each device looks up the array's device address (one host-side query,
+ *     with that device current); make that first call before starting any stream capture;
+ *   - all calls on one device share the array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering between them) race on it.  Calls on one stream are safe;
+ *     the parts that must start from zero are cleared at the start of every call;
+ *   - nothing is allocated or freed, here or in any library routine this call uses.
+ */
+#define NPA_STATIC_SCRATCH_BYTES (8u << 20)
+int npa_grid_build_static(const npa_grid *g, const float *x, int32_t *permutation,
+                          int32_t *bin_offsets, int32_t *block_info, void *stream);
+
+/*
  * Reorder into cell order: out[perm[i]] = in[i].  Replaces
  * HashGrid::bin_particles (sph_cuda.cu:1994-2024, kernel apply_permutation
  * :86-123).  Any of the (in, out) pairs may be NULL together to skip it.

@@ -51,6 +51,7 @@ SIGNATURES = {
     "npa_grid_max_blocks": (_I64, [_P]),
     "npa_grid_scratch_bytes": (_I64, [_P]),
     "npa_grid_build": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, _P]),
+    "npa_grid_build_static": (ctypes.c_int, [_P, _P, _P, _P, _P, _P]),
     "npa_bin_particles": (ctypes.c_int, [_P, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "npa_unbin_particles": (ctypes.c_int, [_P, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "npa_count_forward": (ctypes.c_int, [_P, _P, _P, _P, _P, _P]),

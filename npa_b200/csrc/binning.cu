@@ -11,6 +11,8 @@
 //  * cell counts and work-item counts are scanned together in one three-phase
 //    scan, and the work list is written by the scan's last phase.
 // All kernels are HBM-bound integer work; nothing here is GEMM shaped.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace npa {
@@ -426,6 +428,53 @@ int npa_grid_build(const npa_grid *gd, const float *x, int32_t *permutation, int
     if ((rc = check_launch("scatter_kernel")) != NPA_OK) return rc;
     rank_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, bin_offsets, s.order, permutation, g);
     return check_launch("rank_kernel");
+}
+
+}  // extern "C"
+
+// Work arrays of npa_grid_build_static(): a fixed device array owned by the library, so that the
+// call needs no scratch from the caller and allocates nothing.  In host code the symbol is only a
+// handle; its device address is looked up once per device and cached below.
+static __device__ __align__(256) unsigned char g_static_scratch[NPA_STATIC_SCRATCH_BYTES];
+
+namespace npa {
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static void *g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device (queried once per device).
+static int static_scratch_address(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(NPA_ERR_UNSUPPORTED, "device ordinal %d is out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(NPA_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return NPA_OK;
+}
+}  // namespace npa
+
+extern "C" {
+
+int npa_grid_build_static(const npa_grid *gd, const float *x, int32_t *permutation, int32_t *bin_offsets,
+                          int32_t *block_info, void *stream) {
+    const int64_t need = npa_grid_scratch_bytes(gd);
+    if (need < 0) return (int)need;
+    if (need > (int64_t)NPA_STATIC_SCRATCH_BYTES)
+        return fail(NPA_ERR_SCRATCH_TOO_SMALL,
+                    "npa_grid_build_static: this grid needs %lld bytes of work arrays, the built-in array holds %u; "
+                    "use npa_grid_build with caller scratch", (long long)need, (unsigned)NPA_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != NPA_OK) return rc;
+    return npa_grid_build(gd, x, permutation, bin_offsets, block_info, scratch, (int64_t)NPA_STATIC_SCRATCH_BYTES, stream);
 }
 
 int npa_bin_particles(const npa_grid *gd, int32_t channels, const float *x, const float *s,

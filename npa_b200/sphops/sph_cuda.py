@@ -126,6 +126,18 @@ class _HashGridBase:
         self._call(_lib.npa_grid_build, positions, self._ref(), N.ptr(positions), N.ptr(permutation),
                    N.ptr(bin_offsets), N.ptr(block_info), N.ptr(scratch), self._scratch_bytes)
 
+    def initialize_static(self, positions, permutation, bin_offsets, block_info):
+        """``initialize`` without any scratch tensor: the work arrays are a fixed array inside the
+        library (``npa_grid_build_static``).  For hosts that manage all device memory themselves and
+        do not let this package allocate; raises ``RuntimeError`` when the grid needs more than the
+        built-in array holds.  Calls on one device share that array, so keep them on one stream."""
+        self._pos(positions, "positions")
+        _check(bin_offsets, (self._B * self._cells + 1,), "bin_offsets", torch.int32)
+        _check(permutation, (self._B, self._N), "permutation", torch.int32)
+        _check(block_info, (self._max_blocks, 4), "block_info", torch.int32)
+        self._call(_lib.npa_grid_build_static, positions, self._ref(), N.ptr(positions), N.ptr(permutation),
+                   N.ptr(bin_offsets), N.ptr(block_info))
+
     def _permute(self, fn, xin, sin, min_, permutation, xout, sout, mout, names):
         C = sin.shape[2] if isinstance(sin, torch.Tensor) and sin.dim() == 3 else -1
         self._pos(xin, names[0])
