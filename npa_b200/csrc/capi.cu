@@ -2,6 +2,10 @@
 // dispatch into the kernel translation units.  One function per method of the
 // reference's HashGrid class (sphops/sph_cuda.cu:2058-3046) plus the two fused
 // perception calls.
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "ops.cuh"
 
 namespace npa {
@@ -26,6 +30,28 @@ int launch_feature_backward(const Geom &g, int mask, bool full, const FeatureBwd
     if (g.dim == 2) return g.periodic ? NPA_FB(2, true) : NPA_FB(2, false);
     return g.periodic ? NPA_FB(3, true) : NPA_FB(3, false);
 #undef NPA_FB
+}
+
+int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *out) {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void *>, int> cache;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_pair(dev, kernel);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        int sms = 0, per_sm = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess && dyn_smem > 0)
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem);
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "sizing a persistent launch: %s", cudaGetErrorString(e));
+        it = cache.emplace(key, sms * (per_sm > 0 ? per_sm : 1)).first;
+    }
+    *out = it->second;
+    return NPA_OK;
 }
 
 // Common checks of an operator call: geometry, the two snapshot arrays, the

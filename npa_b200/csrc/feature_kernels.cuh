@@ -5,21 +5,31 @@
 // Replaces forward_kernel / backward_kernel of the reference for the Blur and
 // Gradient computation types (sphops/sph_cuda.cu:1699-1716, 1185-1235,
 // 1265-1327).  The reference maps a thread to (particle, feature) and redoes the
-// distance test and the kernel weight once per feature; here a pair is tested
-// once, by one lane, and the accepted pairs of a particle go through a small
-// per-warp shared-memory list that the particle's LPP lanes then walk with VW
-// features each (128-bit feature loads when C % 4 == 0).
+// distance test and the kernel weight once per feature.  Here one warp owns one
+// work item and walks its particles one at a time in three stages:
+//   1. test: the 32 lanes test 32 candidates per round and ballot-compact the
+//      accepted displacements into a per-warp shared-memory list;
+//   2. weights: the lanes turn list entries into pair scalars (kernel weight,
+//      spiky factors, m_j / rho_j), one entry per lane, all lanes busy;
+//   3. drain: the warp is split into 32 / LPP sub-groups of LPP lanes; each
+//      sub-group takes every (32 / LPP)-th pair and its lanes cover the features
+//      (VW = 4 per lane, 128-bit loads when C % 4 == 0).  Sub-group partial sums
+//      are combined by shuffles once per particle.
+// Every pair is tested once and its scalars are computed once; the work of a
+// particle is spread evenly over the warp whatever its neighbour count.
 //
 // Backward is a gather (no global atomics): particle i collects the terms of
 // both roles it plays in each pair.  Sums over features (the position and
-// density gradients) stay lane-local until one sub-group reduction at the end.
+// density gradients) stay lane-local until the final reduction.
 #pragma once
 #include "neighbors.cuh"
 #include "ops.cuh"
 
 namespace npa {
 
-constexpr int kListPerWarp = 128;  // accepted-pair slots per warp, split evenly between its sub-groups
+constexpr int kListPerWarp = 128;  // accepted-pair slots per warp
+constexpr int kFwdStages = 4;       // pairs fetched ahead per sub-group, forward
+constexpr int kBwdStages = 3;       // same, backward (five pieces per pair)
 
 template <int VW>
 __device__ inline void load_feat(const float *__restrict__ p, float (&v)[VW]) {
@@ -59,32 +69,98 @@ __device__ inline void store_run(float *__restrict__ p, const float (&v)[NF]) {
     }
 }
 
+// 4-, 8- or 16-byte asynchronous global -> shared copy (cp.async, L1-allocating).  Each lane
+// copies only what it will read back itself, so completion is tracked per thread with
+// cp.async.wait_group and no barrier or cross-lane flag is involved.
+template <int BYTES>
+__device__ inline void async_copy(void *smem_dst, const void *gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(gmem_src), "n"(BYTES) : "memory");
+}
+__device__ inline void async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int PENDING>
+__device__ inline void async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(PENDING) : "memory"); }
+
+// VW floats per lane: the element type of a lane's staging slot.
+template <int VW> struct Piece { float v[VW]; };
+template <> struct __align__(16) Piece<4> { float v[4]; };
+
+// Number of CTAs of a persistent launch of `kernel`: every SM filled to the kernel's occupancy.
+// Cached per (device, kernel); the first call also raises the kernel's dynamic shared-memory
+// limit to what its staging ring needs.  Defined in capi.cu.
+int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *out);
+template <typename Kernel>
+int persistent_ctas(Kernel kernel, int threads, size_t dyn_smem, int *out) {
+    return persistent_ctas_impl(reinterpret_cast<const void *>(kernel), threads, dyn_smem, out);
+}
+
+// Sum over the sub-groups of a warp: lanes with equal (lane % LPP) are combined.
+template <int LPP>
+__device__ inline float across_subgroups(float v) {
+#pragma unroll
+    for (int o = LPP; o < 32; o <<= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+// Stage 1 for one particle: test every candidate of every range, append the
+// accepted displacements (r, index of j) to `geo`; calls flush(n) whenever the
+// list could overflow and once at the end.
+template <int D, bool PER, typename Flush>
+__device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
+                                     const int4 *rng, int nr, float4 *geo, Flush &&flush) {
+    const int lane = threadIdx.x & 31;
+    int n = 0;
+    for (int r = 0; r < nr; ++r) {
+        const int4 rg = rng[r];
+        const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
+        for (int j0 = rg.x; j0 < rg.y; j0 += 32) {
+            const int j = j0 + lane;
+            float rx = 0.f, ry = 0.f, rz = 0.f;
+            bool acc = false;
+            if (j < rg.y) {
+                const Pos<D> pj = load_pos<D>(x, j);
+                acc = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz) < g.h2;
+            }
+            const unsigned bal = __ballot_sync(kFull, acc);
+            if (acc) geo[n + __popc(bal & ((1u << lane) - 1u))] = make_float4(rx, ry, rz, __int_as_float(j));
+            n += __popc(bal);
+            if (n + 32 > kListPerWarp) {
+                flush(n);
+                n = 0;
+            }
+        }
+    }
+    flush(n);
+}
+
 template <int D, bool PER, int LPP, int VW, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 feature_forward_kernel(FeatureFwdArgs a, Geom g) {
-    constexpr int PPW = 32 / LPP;
-    constexpr int CAP = kListPerWarp / PPW;
-    constexpr unsigned SUBMASK = LPP == 32 ? 0xffffffffu : ((1u << LPP) - 1u);
+    constexpr int PP = 32 / LPP;  // pairs drained in parallel
+    constexpr int S = kFwdStages;
     __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
-    __shared__ float4 s_ent[kWarpsPerCta][kListPerWarp];
-    __shared__ int s_idx[kWarpsPerCta][kListPerWarp];
+    __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z, index of j
+    __shared__ float4 s_ent[kWarpsPerCta][kListPerWarp];  // v_j K.x, v_j K.y, v_j K.z, v_j W
+    extern __shared__ __align__(16) unsigned char s_dyn[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarpsPerCta + warp;
-    if (row >= g.max_blocks) return;
-    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
-    if (it.count <= 0) return;
+    const int sg = lane / LPP, sl = lane % LPP;
     int4 *rng = s_ranges[warp];
-    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
-    const int sub = lane / LPP, sl = lane % LPP;
-    float4 *ent = s_ent[warp] + sub * CAP;
-    int *idx = s_idx[warp] + sub * CAP;
+    float4 *geo = s_geo[warp];
+    float4 *ent = s_ent[warp];
+    // lane-private staging ring for the neighbour's feature piece: [stage][lane]
+    Piece<VW> *ring = reinterpret_cast<Piece<VW> *>(s_dyn) + (size_t)warp * S * 32 + lane;
     const int C = a.C;
 
-    for (int k0 = 0; k0 < it.count; k0 += PPW) {
-        const int k = k0 + sub;
-        const bool ivalid = k < it.count;
-        const long long i = it.first + (ivalid ? k : 0);
+    // persistent warps: consecutive rows go to the warps of one CTA, then to the next CTA
+    for (int row = blockIdx.x * kWarpsPerCta + warp; row < g.max_blocks; row += gridDim.x * kWarpsPerCta) {
+    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+    if (it.count <= 0) break;  // rows after the last work item are zero
+    __syncwarp();
+    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+
+    for (int k = 0; k < it.count; ++k) {
+        const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
         for (int fbase = 0; fbase < C; fbase += LPP * VW) {
             const int f0 = fbase + sl * VW;
@@ -94,18 +170,48 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             for (int q = 0; q < VW; ++q) { si[q] = 0.f; blur[q] = 0.f; }
 #pragma unroll
             for (int q = 0; q < VW * D; ++q) gr[q] = 0.f;
-            if (ivalid && fvalid && (MASK & F_GRAD)) load_feat<VW>(a.s + i * C + f0, si);
-            int n_sub = 0;
+            if (fvalid && (MASK & F_GRAD)) load_feat<VW>(a.s + i * C + f0, si);
 
-            auto drain = [&]() {
+            auto flush = [&](int n) {
                 __syncwarp();
-                const int nmax = __reduce_max_sync(kFull, n_sub);
-                for (int e = 0; e < nmax; ++e) {
-                    if (e < n_sub && fvalid) {
+                for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
+                    const float4 ge = geo[e];
+                    const int j = __float_as_int(ge.w);
+                    const float q = sq_norm<D>(ge.x, ge.y, ge.z);
+                    const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
+                    const float vj = mj / __ldg(a.rho + j);
+                    float wv = 0.f, kv = 0.f;
+                    if (MASK & F_BLUR) {
+                        const float t = fmaxf(g.h2 - q, 0.f);
+                        wv = vj * (t * t * t);
+                    }
+                    if ((MASK & F_GRAD) && q > 0.f) {
+                        float dist;
+                        kv = vj * spiky_phi(q, g.h, dist);
+                    }
+                    ent[e] = make_float4(kv * ge.x, kv * ge.y, kv * ge.z, wv);
+                }
+                __syncwarp();
+                if (fvalid) {
+                    // stage 3: each sub-group drains every PP-th pair; the neighbour's features are
+                    // fetched S pairs ahead with cp.async into this lane's ring
+                    auto fetch = [&](int e, int slot) {
+                        if (e < n) {
+                            const long long j = __float_as_int(geo[e].w);
+                            async_copy<VW * 4>(ring + slot * 32, a.s + j * C + f0);
+                        }
+                        async_commit();
+                    };
+#pragma unroll
+                    for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
+                    int slot = 0;
+                    for (int e = sg; e < n; e += PP) {
                         const float4 en = ent[e];
-                        const long long j = idx[e];
+                        async_wait<S - 1>();
+                        const Piece<VW> pj = ring[slot * 32];
                         float sj[VW];
-                        load_feat<VW>(a.s + j * C + f0, sj);
+#pragma unroll
+                        for (int q = 0; q < VW; ++q) sj[q] = pj.v[q];
 #pragma unroll
                         for (int q = 0; q < VW; ++q) {
                             if (MASK & F_BLUR) blur[q] = fmaf(en.w, sj[q], blur[q]);
@@ -116,96 +222,67 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                                 if (D == 3) gr[q * D + 2] = fmaf(df, en.z, gr[q * D + 2]);
                             }
                         }
+                        // refill the slot only after its values were consumed by the arithmetic above
+                        fetch(e + S * PP, slot);
+                        slot = slot + 1 == S ? 0 : slot + 1;
                     }
+                    async_wait<0>();
                 }
-                n_sub = 0;
                 __syncwarp();
             };
+            collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
 
-            for (int r = 0; r < nr; ++r) {
-                const int4 rg = rng[r];
-                const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-                for (int j0 = rg.x; j0 < rg.y; j0 += LPP) {
-                    const int j = j0 + sl;
-                    float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
-                    bool acc = false;
-                    if (ivalid && j < rg.y) {
-                        const Pos<D> pj = load_pos<D>(a.x, j);
-                        q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
-                        acc = q < g.h2;
-                    }
-                    const unsigned bal = __ballot_sync(kFull, acc);
-                    const unsigned sb = (bal >> (sub * LPP)) & SUBMASK;
-                    if (acc) {
-                        const int pos = n_sub + __popc(sb & ((1u << sl) - 1u));
-                        const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
-                        const float vj = mj / __ldg(a.rho + j);
-                        float wv = 0.f, kv = 0.f;
-                        if (MASK & F_BLUR) {
-                            const float t = fmaxf(g.h2 - q, 0.f);
-                            wv = vj * (t * t * t);
-                        }
-                        if ((MASK & F_GRAD) && q > 0.f) {
-                            float dist;
-                            kv = vj * spiky_phi(q, g.h, dist);
-                        }
-                        ent[pos] = make_float4(kv * rx, kv * ry, kv * rz, wv);
-                        idx[pos] = j;
-                    }
-                    n_sub += __popc(sb);
-                    if (__any_sync(kFull, n_sub + LPP > CAP)) drain();
-                }
+            if (MASK & F_BLUR) {
+#pragma unroll
+                for (int q = 0; q < VW; ++q) blur[q] = g.c_s * across_subgroups<LPP>(blur[q]);
             }
-            drain();
-
-            if (ivalid && fvalid) {
-                if ((MASK & F_BLUR) && a.blur) {
+            if (MASK & F_GRAD) {
 #pragma unroll
-                    for (int q = 0; q < VW; ++q) blur[q] *= g.c_s;
-                    store_run<VW, VW>(a.blur + i * C + f0, blur);
-                }
-                if ((MASK & F_GRAD) && a.grad) {
-#pragma unroll
-                    for (int q = 0; q < VW * D; ++q) gr[q] *= g.c_g;
-                    store_run<VW, VW * D>(a.grad + (i * C + f0) * D, gr);
-                }
+                for (int q = 0; q < VW * D; ++q) gr[q] = g.c_g * across_subgroups<LPP>(gr[q]);
+            }
+            if (sg == 0 && fvalid) {
+                if ((MASK & F_BLUR) && a.blur) store_run<VW, VW>(a.blur + i * C + f0, blur);
+                if ((MASK & F_GRAD) && a.grad) store_run<VW, VW * D>(a.grad + (i * C + f0) * D, gr);
             }
         }
     }
+    }  // rows
 }
 
 template <int D, bool PER, int LPP, int VW, int MASK, bool FULL>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 feature_backward_kernel(FeatureBwdArgs a, Geom g) {
-    constexpr int PPW = 32 / LPP;
-    constexpr int CAP = kListPerWarp / PPW;
-    constexpr unsigned SUBMASK = LPP == 32 ? 0xffffffffu : ((1u << LPP) - 1u);
+    constexpr int PP = 32 / LPP;
     __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
-    __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z v_j
+    __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z, index of j
     __shared__ float4 s_ker[kWarpsPerCta][kListPerWarp];  // W, 6(h^2-q)^2, phi, psi
-    __shared__ int s_idx[kWarpsPerCta][kListPerWarp];
+    __shared__ float s_vol[kWarpsPerCta][kListPerWarp];   // v_j = m_j / rho_j
+    extern __shared__ __align__(16) unsigned char s_dyn[];
+    constexpr int S = kBwdStages;
+    constexpr int NP = 2 + D;  // pieces per pair and lane: s_j, dL/dblur_j, D pieces of dL/dgrad_j
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarpsPerCta + warp;
-    if (row >= g.max_blocks) return;
-    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
-    if (it.count <= 0) return;
+    const int sg = lane / LPP, sl = lane % LPP;
     int4 *rng = s_ranges[warp];
-    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
-    const int sub = lane / LPP, sl = lane % LPP;
-    float4 *geo = s_geo[warp] + sub * CAP;
-    float4 *ker = s_ker[warp] + sub * CAP;
-    int *idx = s_idx[warp] + sub * CAP;
+    float4 *geo = s_geo[warp];
+    float4 *ker = s_ker[warp];
+    float *vol = s_vol[warp];
+    // lane-private staging ring: [stage][piece][lane]
+    Piece<VW> *ring = reinterpret_cast<Piece<VW> *>(s_dyn) + (size_t)warp * S * NP * 32 + lane;
     const int C = a.C;
 
-    for (int k0 = 0; k0 < it.count; k0 += PPW) {
-        const int k = k0 + sub;
-        const bool ivalid = k < it.count;
-        const long long i = it.first + (ivalid ? k : 0);
+    for (int row = blockIdx.x * kWarpsPerCta + warp; row < g.max_blocks; row += gridDim.x * kWarpsPerCta) {
+    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+    if (it.count <= 0) break;  // rows after the last work item are zero
+    __syncwarp();
+    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+
+    for (int k = 0; k < it.count; ++k) {
+        const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
         const float mi = a.mass ? __ldg(a.mass + i) : 1.0f;
         const float vi = mi / __ldg(a.rho + i);
-        // lane-partial sums over this lane's features, reduced across the sub-group at the end
+        // lane-partial sums over this lane's features and pairs, reduced over the whole warp at the end
         float dxs[3] = {0.f, 0.f, 0.f}, dxg[3] = {0.f, 0.f, 0.f}, drs = 0.f, drg = 0.f;
 
         for (int fbase = 0; fbase < C; fbase += LPP * VW) {
@@ -216,28 +293,70 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             for (int q = 0; q < VW; ++q) { si[q] = 0.f; gbi[q] = 0.f; ds[q] = 0.f; dsg[q] = 0.f; }
 #pragma unroll
             for (int q = 0; q < VW * D; ++q) ggi[q] = 0.f;
-            if (ivalid && fvalid) {
+            if (fvalid) {
                 if (FULL) load_feat<VW>(a.s + i * C + f0, si);
                 if (FULL && (MASK & F_BLUR)) load_feat<VW>(a.g_blur + i * C + f0, gbi);
                 if (MASK & F_GRAD) load_run<VW, VW * D>(a.g_grad + (i * C + f0) * D, ggi);
             }
-            int n_sub = 0;
 
-            auto drain = [&]() {
+            auto flush = [&](int n) {
                 __syncwarp();
-                const int nmax = __reduce_max_sync(kFull, n_sub);
-                for (int e = 0; e < nmax; ++e) {
-                    if (e < n_sub && fvalid) {
+                for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
+                    const float4 ge = geo[e];
+                    const int j = __float_as_int(ge.w);
+                    const float q = sq_norm<D>(ge.x, ge.y, ge.z);
+                    const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
+                    const float t = fmaxf(g.h2 - q, 0.f);
+                    float phi = 0.f, psi = 0.f;
+                    if ((MASK & F_GRAD) && q > 0.f) {
+                        float dist;
+                        phi = spiky_phi(q, g.h, dist);
+                        if (FULL) psi = spiky_psi(dist, g.h);
+                    }
+                    ker[e] = make_float4(t * t * t, 6.0f * t * t, phi, psi);
+                    vol[e] = mj / __ldg(a.rho + j);
+                }
+                __syncwarp();
+                if (fvalid) {
+                    // stage 3: each sub-group drains every PP-th pair; the neighbour's rows are fetched
+                    // S pairs ahead with cp.async into this lane's ring
+                    auto fetch = [&](int e, int slot) {
+                        if (e < n) {
+                            const long long j = __float_as_int(geo[e].w);
+                            Piece<VW> *dst = ring + slot * NP * 32;
+                            if (FULL) async_copy<VW * 4>(dst, a.s + j * C + f0);
+                            if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + j * C + f0);
+                            if (MASK & F_GRAD) {
+#pragma unroll
+                                for (int d = 0; d < D; ++d)
+                                    async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (j * C + f0) * D + d * VW);
+                            }
+                        }
+                        async_commit();
+                    };
+#pragma unroll
+                    for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
+                    int slot = 0;
+                    for (int e = sg; e < n; e += PP) {
                         const float4 e0 = geo[e];
                         const float4 e1 = ker[e];
-                        const long long j = idx[e];
+                        const float vj = vol[e];
                         const float rv[3] = {e0.x, e0.y, e0.z};
-                        const float vj = e0.w;
+                        async_wait<S - 1>();
+                        const Piece<VW> *src = ring + slot * NP * 32;
                         float sj[VW];
-                        if (FULL) load_feat<VW>(a.s + j * C + f0, sj);
+                        if (FULL) {
+                            const Piece<VW> t = src[0];
+#pragma unroll
+                            for (int q = 0; q < VW; ++q) sj[q] = t.v[q];
+                        }
                         if (MASK & F_BLUR) {
                             float gbj[VW];
-                            load_feat<VW>(a.g_blur + j * C + f0, gbj);
+                            {
+                                const Piece<VW> t = src[32];
+#pragma unroll
+                                for (int q = 0; q < VW; ++q) gbj[q] = t.v[q];
+                            }
                             float A = 0.f, Bp = 0.f;
 #pragma unroll
                             for (int q = 0; q < VW; ++q) {
@@ -256,7 +375,12 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                         }
                         if (MASK & F_GRAD) {
                             float ggj[VW * D];
-                            load_run<VW, VW * D>(a.g_grad + (j * C + f0) * D, ggj);
+#pragma unroll
+                            for (int d = 0; d < D; ++d) {
+                                const Piece<VW> t = src[(2 + d) * 32];
+#pragma unroll
+                                for (int q = 0; q < VW; ++q) ggj[d * VW + q] = t.v[q];
+                            }
                             float kvec[3];
 #pragma unroll
                             for (int d = 0; d < D; ++d) kvec[d] = e1.z * rv[d];
@@ -285,61 +409,31 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                                 for (int d = 0; d < D; ++d) dxg[d] += e1.z * u[d] - sc * rv[d];
                             }
                         }
+                        // refill the slot only after its values were consumed by the arithmetic above
+                        fetch(e + S * PP, slot);
+                        slot = slot + 1 == S ? 0 : slot + 1;
                     }
+                    async_wait<0>();
                 }
-                n_sub = 0;
                 __syncwarp();
             };
+            collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
 
-            for (int r = 0; r < nr; ++r) {
-                const int4 rg = rng[r];
-                const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-                for (int j0 = rg.x; j0 < rg.y; j0 += LPP) {
-                    const int j = j0 + sl;
-                    float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
-                    bool acc = false;
-                    if (ivalid && j < rg.y) {
-                        const Pos<D> pj = load_pos<D>(a.x, j);
-                        q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
-                        acc = q < g.h2;
-                    }
-                    const unsigned bal = __ballot_sync(kFull, acc);
-                    const unsigned sb = (bal >> (sub * LPP)) & SUBMASK;
-                    if (acc) {
-                        const int pos = n_sub + __popc(sb & ((1u << sl) - 1u));
-                        const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
-                        const float vj = mj / __ldg(a.rho + j);
-                        const float t = fmaxf(g.h2 - q, 0.f);
-                        float phi = 0.f, psi = 0.f;
-                        if ((MASK & F_GRAD) && q > 0.f) {
-                            float dist;
-                            phi = spiky_phi(q, g.h, dist);
-                            if (FULL) psi = spiky_psi(dist, g.h);
-                        }
-                        geo[pos] = make_float4(rx, ry, rz, vj);
-                        ker[pos] = make_float4(t * t * t, 6.0f * t * t, phi, psi);
-                        idx[pos] = j;
-                    }
-                    n_sub += __popc(sb);
-                    if (__any_sync(kFull, n_sub + LPP > CAP)) drain();
-                }
-            }
-            drain();
-
-            if (ivalid && fvalid && a.grad_s) {
+            if (a.grad_s) {
                 float out[VW];
 #pragma unroll
-                for (int q = 0; q < VW; ++q) out[q] = g.c_s * vi * ds[q] - g.c_g * dsg[q];
-                store_run<VW, VW>(a.grad_s + i * C + f0, out);
+                for (int q = 0; q < VW; ++q)
+                    out[q] = across_subgroups<LPP>(g.c_s * vi * ds[q] - g.c_g * dsg[q]);
+                if (sg == 0 && fvalid) store_run<VW, VW>(a.grad_s + i * C + f0, out);
             }
         }
 
         if (FULL) {
             float out[3];
 #pragma unroll
-            for (int d = 0; d < D; ++d) out[d] = subgroup_sum<LPP>(g.c_s * dxs[d] + g.c_g * dxg[d]);
-            const float dr = subgroup_sum<LPP>(g.c_g * drg - g.c_s * drs);
-            if (ivalid && sl == 0) {
+            for (int d = 0; d < D; ++d) out[d] = subgroup_sum<32>(g.c_s * dxs[d] + g.c_g * dxg[d]);
+            const float dr = subgroup_sum<32>(g.c_g * drg - g.c_s * drs);
+            if (lane == 0) {
                 if (a.grad_x) {
                     if (D == 2) reinterpret_cast<float2 *>(a.grad_x)[i] = make_float2(out[0], out[1]);
                     else reinterpret_cast<float4 *>(a.grad_x)[i] = make_float4(out[0], out[1], out[2], 0.f);
@@ -348,6 +442,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             }
         }
     }
+    }  // rows
 }
 
 // ---------------------------------------------------------------------------
@@ -361,19 +456,29 @@ inline bool feature_rows_vectorisable(int C, const void *p0, const void *p1, con
     return C % 4 == 0 && bits % 16 == 0;
 }
 
+template <int VW, typename Kernel>
+int launch_feature_forward_mask(const Geom &g, Kernel kernel, const FeatureFwdArgs &a, cudaStream_t st) {
+    const int threads = kWarpsPerCta * 32;
+    const size_t dyn = (size_t)kWarpsPerCta * kFwdStages * 32 * sizeof(Piece<VW>);
+    int ctas = 0;
+    int rc = persistent_ctas(kernel, threads, dyn, &ctas);
+    if (rc != NPA_OK) return rc;
+    const int needed = (g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta;
+    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
+    return check_launch("feature_forward_kernel");
+}
+
 template <int D, bool PER, int LPP, int VW>
 int launch_feature_forward_shape(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
-    const unsigned threads = kWarpsPerCta * 32;
     switch (mask) {
-        case F_BLUR: feature_forward_kernel<D, PER, LPP, VW, F_BLUR><<<blocks, threads, 0, st>>>(a, g); break;
-        case F_GRAD: feature_forward_kernel<D, PER, LPP, VW, F_GRAD><<<blocks, threads, 0, st>>>(a, g); break;
+        case F_BLUR:
+            return launch_feature_forward_mask<VW>(g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR>, a, st);
+        case F_GRAD:
+            return launch_feature_forward_mask<VW>(g, feature_forward_kernel<D, PER, LPP, VW, F_GRAD>, a, st);
         case F_BLUR | F_GRAD:
-            feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD><<<blocks, threads, 0, st>>>(a, g);
-            break;
+            return launch_feature_forward_mask<VW>(g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD>, a, st);
         default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported feature forward mask %d", mask);
     }
-    return check_launch("feature_forward_kernel");
 }
 
 template <int D, bool PER>
@@ -389,23 +494,29 @@ int launch_feature_forward_geom(const Geom &g, int mask, const FeatureFwdArgs &a
     return launch_feature_forward_shape<D, PER, 32, 1>(g, mask, a, st);
 }
 
+template <int D, int VW, typename Kernel>
+int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdArgs &a, cudaStream_t st) {
+    const int threads = kWarpsPerCta * 32;
+    const size_t dyn = (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>);
+    int ctas = 0;
+    int rc = persistent_ctas(kernel, threads, dyn, &ctas);
+    if (rc != NPA_OK) return rc;
+    const int needed = (g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta;
+    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
+    return check_launch("feature_backward_kernel");
+}
+
 template <int D, bool PER, int LPP, int VW, bool FULL>
 int launch_feature_backward_shape(const Geom &g, int mask, const FeatureBwdArgs &a, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
-    const unsigned threads = kWarpsPerCta * 32;
     switch (mask) {
         case F_BLUR:
-            feature_backward_kernel<D, PER, LPP, VW, F_BLUR, FULL><<<blocks, threads, 0, st>>>(a, g);
-            break;
+            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR, FULL>, a, st);
         case F_GRAD:
-            feature_backward_kernel<D, PER, LPP, VW, F_GRAD, FULL><<<blocks, threads, 0, st>>>(a, g);
-            break;
+            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_GRAD, FULL>, a, st);
         case F_BLUR | F_GRAD:
-            feature_backward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD, FULL><<<blocks, threads, 0, st>>>(a, g);
-            break;
+            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD, FULL>, a, st);
         default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported feature backward mask %d", mask);
     }
-    return check_launch("feature_backward_kernel");
 }
 
 template <int D, bool PER, bool FULL>
