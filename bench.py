@@ -95,6 +95,7 @@ def cpu_oracle_step(w, x, s, ups, systems):
 def cpu_baseline(w, x, s, ups, repeats=1):
     import oracle
 
+    oracle.set_threads(os.cpu_count() or 1)
     systems = 1
     cpu_oracle_step(w, x, s, ups, systems)  # warm-up (page-in, thread pool)
     times = [cpu_oracle_step(w, x, s, ups, systems) for _ in range(repeats)]
@@ -112,6 +113,7 @@ def run_reference_arm(args, w):
     import oracle
     from npa_b200.workloads import make_inputs
 
+    oracle.set_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1; use every host core
     x, s, ups = make_inputs(w, seed=0)
     systems = 1
     for _ in range(max(1, min(args.warmup, 2))):

@@ -147,6 +147,15 @@ __device__ inline float sq_norm(float rx, float ry, float rz) {
     return q;
 }
 
+// Same quantity with fused multiply-adds, for kernels whose outputs are continuous in r^2
+// (everything except the neighbour count).
+template <int D>
+__device__ inline float sq_norm_fast(float rx, float ry, float rz) {
+    float q = fmaf(ry, ry, rx * rx);
+    if (D == 3) q = fmaf(rz, rz, q);
+    return q;
+}
+
 // Spiky pair factors for 0 < q < h2: phi = 3 (h - d)^2 / d with
 // d = sqrt(q + 1e-12), so that K(r) = phi * r; psi = 3 (h^2 - d^2) / d^3 so that
 // dK/dr = phi * I - psi * r r^T.

@@ -104,23 +104,39 @@ __device__ inline float across_subgroups(float v) {
 
 // Stage 1 for one particle: test every candidate of every range, append the
 // accepted displacements (r, index of j) to `geo`; calls flush(n) whenever the
-// list could overflow and once at the end.
+// list could overflow and once at the end.  The position of the next round's
+// candidate is loaded before the current round is tested, so the load latency
+// overlaps the test.
 template <int D, bool PER, typename Flush>
 __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
                                      const int4 *rng, int nr, float4 *geo, Flush &&flush) {
     const int lane = threadIdx.x & 31;
     int n = 0;
-    for (int r = 0; r < nr; ++r) {
-        const int4 rg = rng[r];
-        const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-        for (int j0 = rg.x; j0 < rg.y; j0 += 32) {
+    if (nr > 0) {
+        int r = 0;
+        int4 rg = rng[0];
+        int j0 = rg.x;
+        Pos<D> pj = {0.f, 0.f, 0.f};
+        if (j0 + lane < rg.y) pj = load_pos<D>(x, j0 + lane);
+        Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
+        while (true) {
+            // locate and prefetch the next round
+            int nxt_r = r, nxt_j0 = j0 + 32;
+            int4 nxt_rg = rg;
+            if (nxt_j0 >= rg.y) {
+                nxt_r = r + 1;
+                if (nxt_r < nr) {
+                    nxt_rg = rng[nxt_r];
+                    nxt_j0 = nxt_rg.x;
+                }
+            }
+            Pos<D> pn = {0.f, 0.f, 0.f};
+            if (nxt_r < nr && nxt_j0 + lane < nxt_rg.y) pn = load_pos<D>(x, nxt_j0 + lane);
+            // test the current round
             const int j = j0 + lane;
             float rx = 0.f, ry = 0.f, rz = 0.f;
             bool acc = false;
-            if (j < rg.y) {
-                const Pos<D> pj = load_pos<D>(x, j);
-                acc = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz) < g.h2;
-            }
+            if (j < rg.y) acc = displacement<D, PER, false>(g, org, pj.x, pj.y, pj.z, rx, ry, rz) < g.h2;
             const unsigned bal = __ballot_sync(kFull, acc);
             if (acc) geo[n + __popc(bal & ((1u << lane) - 1u))] = make_float4(rx, ry, rz, __int_as_float(j));
             n += __popc(bal);
@@ -128,6 +144,9 @@ __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x,
                 flush(n);
                 n = 0;
             }
+            if (nxt_r >= nr) break;
+            if (PER && nxt_r != r) org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, nxt_rg.z);
+            r = nxt_r; rg = nxt_rg; j0 = nxt_j0; pj = pn;
         }
     }
     flush(n);
@@ -177,7 +196,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
                     const float4 ge = geo[e];
                     const int j = __float_as_int(ge.w);
-                    const float q = sq_norm<D>(ge.x, ge.y, ge.z);
+                    const float q = sq_norm_fast<D>(ge.x, ge.y, ge.z);
                     const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                     const float vj = mj / __ldg(a.rho + j);
                     float wv = 0.f, kv = 0.f;
@@ -197,8 +216,8 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     // fetched S pairs ahead with cp.async into this lane's ring
                     auto fetch = [&](int e, int slot) {
                         if (e < n) {
-                            const long long j = __float_as_int(geo[e].w);
-                            async_copy<VW * 4>(ring + slot * 32, a.s + j * C + f0);
+                            const int j = __float_as_int(geo[e].w);
+                            async_copy<VW * 4>(ring + slot * 32, a.s + ((long long)j * C + f0));
                         }
                         async_commit();
                     };
@@ -304,7 +323,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
                     const float4 ge = geo[e];
                     const int j = __float_as_int(ge.w);
-                    const float q = sq_norm<D>(ge.x, ge.y, ge.z);
+                    const float q = sq_norm_fast<D>(ge.x, ge.y, ge.z);
                     const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                     const float t = fmaxf(g.h2 - q, 0.f);
                     float phi = 0.f, psi = 0.f;
@@ -322,14 +341,14 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                     // S pairs ahead with cp.async into this lane's ring
                     auto fetch = [&](int e, int slot) {
                         if (e < n) {
-                            const long long j = __float_as_int(geo[e].w);
+                            const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
                             Piece<VW> *dst = ring + slot * NP * 32;
-                            if (FULL) async_copy<VW * 4>(dst, a.s + j * C + f0);
-                            if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + j * C + f0);
+                            if (FULL) async_copy<VW * 4>(dst, a.s + row);
+                            if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + row);
                             if (MASK & F_GRAD) {
 #pragma unroll
                                 for (int d = 0; d < D; ++d)
-                                    async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (j * C + f0) * D + d * VW);
+                                    async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (row * D + d * VW));
                             }
                         }
                         async_commit();

@@ -173,7 +173,7 @@ __device__ inline Pos<D> load_pos(const float *__restrict__ x, long long idx) {
 }
 
 // r = x_j - x_i (minimum image when PER) and q = |r|^2.
-template <int D, bool PER>
+template <int D, bool PER, bool EXACT = true>
 __device__ inline float displacement(const Geom &g, const Origin<D, PER> &o, float jx, float jy, float jz,
                                      float &rx, float &ry, float &rz) {
     rx = jx - o.x[0];
@@ -187,7 +187,7 @@ __device__ inline float displacement(const Geom &g, const Origin<D, PER> &o, flo
         if (fabsf(ry) > g.halfL[1]) ry = wrap_general(ry, g.L[1], g.Llo[1], g.invL[1]);
         if (D == 3 && fabsf(rz) > g.halfL[2]) rz = wrap_general(rz, g.L[2], g.Llo[2], g.invL[2]);
     }
-    return sq_norm<D>(rx, ry, rz);
+    return EXACT ? sq_norm<D>(rx, ry, rz) : sq_norm_fast<D>(rx, ry, rz);
 }
 
 // Sum over the LPP lanes of a sub-group (LPP a power of two <= 32).
