@@ -236,11 +236,14 @@ int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
  * The two feature operators share every pair test and every neighbour feature
  * load, so one sweep produces both.  Results equal npa_blur_* / npa_gradient_*
  * (sph_cuda.cu:2191-2365 forward, :2580-2728 and :2810-2958 backward); either
- * output (forward) or upstream gradient (backward) may be NULL.               */
+ * output (forward) or upstream gradient (backward) may be NULL.  `moment`
+ * [B,N,D,D] (may be NULL) additionally returns the moment matrix
+ * (npa_moment_matrix_forward), which shares every pair factor with the
+ * gradient; it needs both s_blur and s_grad.                                  */
 int npa_blur_gradient_forward(const npa_grid *g, int32_t channels, const float *x_bin,
                               const float *rho, const float *mass, const float *s_bin,
-                              float *s_blur, float *s_grad, const int32_t *bin_offsets,
-                              const int32_t *block_info, void *stream);
+                              float *s_blur, float *s_grad, float *moment,
+                              const int32_t *bin_offsets, const int32_t *block_info, void *stream);
 
 /* grad_x == NULL and grad_rho == NULL selects the variant that differentiates
  * with respect to s only. */

@@ -10,11 +10,13 @@ import sys
 __version__ = "0.1.0"
 
 
-def install_as_sphops():
+def install_as_sphops(fuse=False):
     """Register ``npa_b200.sphops`` under the top-level name ``sphops``.
 
     After this call ``from sphops import HashGrid`` (what the reference's models
-    and trainers do) resolves to the B200 implementation.
+    and trainers do) resolves to the B200 implementation.  ``fuse=True`` also turns
+    on sibling-output fusion of the per-operator API (``sphops.enable_fusion``), which
+    makes ``NPA.perceive`` run two neighbour sweeps instead of five.
     """
     from . import sphops as _sphops
     from .sphops import sph as _sph, sph_cuda as _sph_cuda
@@ -22,4 +24,6 @@ def install_as_sphops():
     sys.modules["sphops"] = _sphops
     sys.modules["sphops.sph"] = _sph
     sys.modules["sphops.sph_cuda"] = _sph_cuda
+    if fuse:
+        _sphops.enable_fusion(True)
     return _sphops

@@ -143,7 +143,7 @@ int npa_blur_forward(const npa_grid *gd, int32_t channels, const float *x_bin, c
     NPA_REQUIRE(rho, "blur_forward", "rho");
     NPA_REQUIRE(s_bin, "blur_forward", "state_in");
     NPA_REQUIRE(s_blur, "blur_forward", "state_out");
-    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, nullptr, channels, bin_offsets, block_info};
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, nullptr, channels, bin_offsets, block_info, nullptr};
     return launch_feature_forward(g, F_BLUR, a, (cudaStream_t)stream);
 }
 
@@ -157,7 +157,7 @@ int npa_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bi
     NPA_REQUIRE(rho, "gradient_forward", "rho");
     NPA_REQUIRE(s_bin, "gradient_forward", "state_in");
     NPA_REQUIRE(s_grad, "gradient_forward", "state_gradient_out");
-    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, nullptr, s_grad, channels, bin_offsets, block_info};
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, nullptr, s_grad, channels, bin_offsets, block_info, nullptr};
     return launch_feature_forward(g, F_GRAD, a, (cudaStream_t)stream);
 }
 
@@ -235,7 +235,7 @@ int npa_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_b
 }
 
 int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
-                              const float *mass, const float *s_bin, float *s_blur, float *s_grad,
+                              const float *mass, const float *s_bin, float *s_blur, float *s_grad, float *moment,
                               const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
     Geom g;
     int rc = begin_op("blur_gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
@@ -243,9 +243,14 @@ int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float 
     if ((rc = check_channels("blur_gradient_forward", channels)) != NPA_OK) return rc;
     NPA_REQUIRE(rho, "blur_gradient_forward", "rho");
     NPA_REQUIRE(s_bin, "blur_gradient_forward", "state_in");
-    const int mask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
+    int mask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
+    if (moment) {
+        if (mask != (F_BLUR | F_GRAD))
+            return fail(NPA_ERR_INVALID_ARGUMENT, "blur_gradient_forward: moment needs both state_out and state_gradient_out");
+        mask |= F_MOMENT;
+    }
     if (!mask) return NPA_OK;
-    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info};
+    FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info, moment};
     return launch_feature_forward(g, mask, a, (cudaStream_t)stream);
 }
 
@@ -299,8 +304,12 @@ int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_
     if (fmask) {
         if ((rc = check_channels("perception_forward", channels)) != NPA_OK) return rc;
         NPA_REQUIRE(s_bin, "perception_forward", "state_in");
-        FeatureFwdArgs fa = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info};
-        if ((rc = launch_feature_forward(g, fmask, fa, st)) != NPA_OK) return rc;
+        // the moment matrix shares every pair scalar with the gradient: fold it into the same sweep
+        const bool fold = moment && fmask == (F_BLUR | F_GRAD);
+        FeatureFwdArgs fa = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info,
+                             fold ? moment : nullptr};
+        if ((rc = launch_feature_forward(g, fold ? (fmask | F_MOMENT) : fmask, fa, st)) != NPA_OK) return rc;
+        if (fold) moment = nullptr;
     }
     if (moment) {
         if (g.dim == 2 && (uintptr_t)moment % 16)

@@ -181,6 +181,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     for (int k = 0; k < it.count; ++k) {
         const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
+        float mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // F_MOMENT: upper triangle, lane-partial over pairs
         for (int fbase = 0; fbase < C; fbase += LPP * VW) {
             const int f0 = fbase + sl * VW;
             const bool fvalid = f0 < C;
@@ -204,9 +205,21 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                         const float t = fmaxf(g.h2 - q, 0.f);
                         wv = vj * (t * t * t);
                     }
-                    if ((MASK & F_GRAD) && q > 0.f) {
+                    if ((MASK & (F_GRAD | F_MOMENT)) && q > 0.f) {
                         float dist;
                         kv = vj * spiky_phi(q, g.h, dist);
+                    }
+                    if ((MASK & F_MOMENT) && fbase == 0) {  // every pair is seen once per feature chunk
+                        mom[0] = fmaf(kv * ge.x, ge.x, mom[0]);
+                        mom[1] = fmaf(kv * ge.x, ge.y, mom[1]);
+                        if (D == 2) {
+                            mom[2] = fmaf(kv * ge.y, ge.y, mom[2]);
+                        } else {
+                            mom[2] = fmaf(kv * ge.x, ge.z, mom[2]);
+                            mom[3] = fmaf(kv * ge.y, ge.y, mom[3]);
+                            mom[4] = fmaf(kv * ge.y, ge.z, mom[4]);
+                            mom[5] = fmaf(kv * ge.z, ge.z, mom[5]);
+                        }
                     }
                     ent[e] = make_float4(kv * ge.x, kv * ge.y, kv * ge.z, wv);
                 }
@@ -262,6 +275,20 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             if (sg == 0 && fvalid) {
                 if ((MASK & F_BLUR) && a.blur) store_run<VW, VW>(a.blur + i * C + f0, blur);
                 if ((MASK & F_GRAD) && a.grad) store_run<VW, VW * D>(a.grad + (i * C + f0) * D, gr);
+            }
+        }
+        if (MASK & F_MOMENT) {
+#pragma unroll
+            for (int q = 0; q < D * (D + 1) / 2; ++q) mom[q] = g.c_g * subgroup_sum<32>(mom[q]);
+            if (lane == 0 && a.moment) {
+                float *o = a.moment + i * (D * D);
+                if (D == 2) {
+                    o[0] = mom[0]; o[1] = mom[1]; o[2] = mom[1]; o[3] = mom[2];
+                } else {
+                    o[0] = mom[0]; o[1] = mom[1]; o[2] = mom[2];
+                    o[3] = mom[1]; o[4] = mom[3]; o[5] = mom[4];
+                    o[6] = mom[2]; o[7] = mom[4]; o[8] = mom[5];
+                }
             }
         }
     }
@@ -496,6 +523,9 @@ int launch_feature_forward_shape(const Geom &g, int mask, const FeatureFwdArgs &
             return launch_feature_forward_mask<VW>(g, feature_forward_kernel<D, PER, LPP, VW, F_GRAD>, a, st);
         case F_BLUR | F_GRAD:
             return launch_feature_forward_mask<VW>(g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD>, a, st);
+        case F_BLUR | F_GRAD | F_MOMENT:
+            return launch_feature_forward_mask<VW>(
+                g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD | F_MOMENT>, a, st);
         default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported feature forward mask %d", mask);
     }
 }

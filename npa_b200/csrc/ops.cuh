@@ -8,7 +8,8 @@ namespace npa {
 // Which per-particle scalar operators a sweep computes.
 enum { S_COUNT = 1, S_DENSITY = 2, S_DGRAD = 4, S_MOMENT = 8 };
 // Which feature operators a sweep computes.
-enum { F_BLUR = 1, F_GRAD = 2 };
+// F_MOMENT (forward only) adds the moment matrix to a blur + gradient sweep.
+enum { F_BLUR = 1, F_GRAD = 2, F_MOMENT = 4 };
 
 struct ScalarFwdArgs {
     const float *x;       // [B,N,P] cell order
@@ -47,6 +48,7 @@ struct FeatureFwdArgs {
     int C;
     const int32_t *bin_offsets;
     const int32_t *block_info;
+    float *moment;       // [B,N,D,D], only with F_MOMENT
 };
 
 struct FeatureBwdArgs {

@@ -17,7 +17,7 @@ inputs that do not require grad are returned as ``None``.
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -58,6 +58,9 @@ class HashGridSnapshot:
     permutation: torch.Tensor
     block_info: torch.Tensor
     dim: int
+    # outputs computed ahead of their call by a fused sweep (see enable_fusion); not part of the
+    # reference's dataclass, defaulted so positional construction still works
+    parked: dict = field(default_factory=dict, repr=False, compare=False)
 
 
 class HashGrid:
@@ -106,6 +109,119 @@ class HashGrid:
             L = torch.tensor(self.grid_size[d] * self.eps, device=x.device)
             cols.append(torch.remainder(x[..., d] + 0.5 * L, L) - 0.5 * L)
         return torch.stack(cols, dim=-1)
+
+
+# ---------------------------------------------------------------------------------------------
+# Operator fusion behind the per-operator API.
+#
+# NPA.perceive (models/npa.py:105-126) calls density, blur, moment_matrix, gradient and
+# density_gradient one after the other with the SAME tensor objects; each is a full sweep over the
+# neighbour cells in the reference.  With fusion enabled, density() also computes the density
+# gradient and blur() also computes the feature gradient and the moment matrix, in the same sweep,
+# and parks the extra outputs on the snapshot; the later call returns the parked tensor when it
+# is made with the very same input objects (identity and version), otherwise it runs its own
+# kernel as usual.  Five sweeps become two, and autograd sees one node per sweep, so the backward
+# is fused too.  Off by default: a caller that only wants blur would pay for the gradient.
+# ---------------------------------------------------------------------------------------------
+_FUSION = {"enabled": False}
+
+
+def enable_fusion(flag=True):
+    """Turn speculative sibling-output fusion of the per-operator API on or off (process wide)."""
+    _FUSION["enabled"] = bool(flag)
+
+
+def fusion_enabled():
+    return _FUSION["enabled"]
+
+
+def _key(*tensors):
+    """Identity + version of the input tensor objects (None allowed); the objects are kept alive."""
+    return tuple((t, None if t is None else t._version) for t in tensors)
+
+
+def _same(key, *tensors):
+    return len(key) == len(tensors) and all(
+        (kt is t) and (t is None or kv == t._version) for (kt, kv), t in zip(key, tensors))
+
+
+def _park(snapshot, name, key, value):
+    snapshot.parked[name] = (key, value)
+
+
+def _claim(snapshot, name, *tensors):
+    entry = snapshot.parked.get(name)
+    if entry is None or not _same(entry[0], *tensors):
+        return None
+    del snapshot.parked[name]
+    return entry[1]
+
+
+class DensityPair(torch.autograd.Function):
+    """density and density_gradient of the same positions in one sweep."""
+
+    @staticmethod
+    def forward(ctx, x_bin, mass, snapshot):
+        B, N = x_bin.shape[:2]
+        rho = torch.empty(B, N, dtype=torch.float32, device=x_bin.device)
+        rho_grad = torch.empty(B, N, snapshot.dim, dtype=torch.float32, device=x_bin.device)
+        snapshot.grid.perception_forward(x_bin, mass, None, rho, None, rho_grad, None, None, None,
+                                         snapshot.bin_offsets, snapshot.block_info)
+        ctx.save_for_backward(x_bin, *([] if mass is None else [mass]))
+        ctx.has_mass = mass is not None
+        ctx.snapshot = snapshot
+        ctx.dLdx = x_bin.requires_grad
+        return rho, rho_grad
+
+    @staticmethod
+    def backward(ctx, g_rho, g_rho_grad):
+        if not ctx.dLdx or (g_rho is None and g_rho_grad is None):
+            return None, None, None
+        saved = ctx.saved_tensors
+        x_bin, mass = saved[0], (saved[1] if ctx.has_mass else None)
+        snap = ctx.snapshot
+        grad_x = torch.empty_like(x_bin)
+        cont = lambda t: None if t is None else t.contiguous()
+        snap.grid.density_chain_backward(x_bin, mass, cont(g_rho), None, cont(g_rho_grad), grad_x, False,
+                                         snap.bin_offsets, snap.block_info)
+        return grad_x, None, None
+
+
+class BlurGradient(torch.autograd.Function):
+    """blur, feature gradient and (not differentiated) moment matrix in one sweep."""
+
+    @staticmethod
+    def forward(ctx, x_bin, s_bin, rho, mass, snapshot):
+        B, N, C = s_bin.shape
+        dev, dim = x_bin.device, snapshot.dim
+        s_blur = torch.empty_like(s_bin)
+        s_grad = torch.empty(B, N, C, dim, dtype=torch.float32, device=dev)
+        moment = torch.empty(B, N, dim, dim, dtype=torch.float32, device=dev)
+        snapshot.grid.blur_gradient_forward(x_bin, rho, mass, s_bin, s_blur, s_grad, snapshot.bin_offsets,
+                                            snapshot.block_info, moment)
+        ctx.save_for_backward(x_bin, s_bin, rho, *([] if mass is None else [mass]))
+        ctx.has_mass = mass is not None
+        ctx.snapshot = snapshot
+        ctx.needs = (x_bin.requires_grad, s_bin.requires_grad, rho.requires_grad)
+        ctx.mark_non_differentiable(moment)
+        return s_blur, s_grad, moment
+
+    @staticmethod
+    def backward(ctx, g_blur, g_grad, _g_moment):
+        saved = ctx.saved_tensors
+        x_bin, s_bin, rho = saved[:3]
+        mass = saved[3] if ctx.has_mass else None
+        dLdx, dLds, dLdrho = ctx.needs
+        if (g_blur is None and g_grad is None) or not (dLdx or dLds or dLdrho):
+            return None, None, None, None, None
+        snap = ctx.snapshot
+        cont = lambda t: None if t is None else t.contiguous()
+        grad_x = torch.empty_like(x_bin) if dLdx else None
+        grad_s = torch.empty_like(s_bin) if dLds else None
+        grad_rho = torch.empty_like(rho) if dLdrho else None
+        snap.grid.blur_gradient_backward(x_bin, rho, mass, s_bin, cont(g_blur), cont(g_grad), grad_x, grad_s,
+                                         grad_rho, snap.bin_offsets, snap.block_info)
+        return grad_x, grad_s, grad_rho, None, None
 
 
 def _zeros_like_shape(shape, dtype, device):
@@ -189,6 +305,10 @@ class Density(torch.autograd.Function):
 
 
 def density(x_bin, snapshot, mass=None):
+    if _FUSION["enabled"]:
+        rho, rho_grad = DensityPair.apply(x_bin, None if mass is None else _default_mass(x_bin, mass), snapshot)
+        _park(snapshot, "density_gradient", _key(x_bin, mass), rho_grad)
+        return rho
     return Density.apply(x_bin, _default_mass(x_bin, mass), snapshot)
 
 
@@ -226,6 +346,12 @@ class Blur(_FeatureOp):
 
 
 def blur(x_bin, rho, s_bin, snapshot, mass=None):
+    if _FUSION["enabled"]:
+        s_blur, s_grad, moment = BlurGradient.apply(
+            x_bin, s_bin, rho, None if mass is None else _default_mass(x_bin, mass), snapshot)
+        _park(snapshot, "gradient", _key(x_bin, rho, s_bin, mass), s_grad)
+        _park(snapshot, "moment_matrix", _key(x_bin, rho, mass), moment)
+        return s_blur
     return Blur.apply(x_bin, s_bin, rho, _default_mass(x_bin, mass), snapshot)
 
 
@@ -240,6 +366,9 @@ class Gradient(_FeatureOp):
 
 
 def gradient(x_bin, rho, s_bin, snapshot, mass=None):
+    parked = _claim(snapshot, "gradient", x_bin, rho, s_bin, mass)
+    if parked is not None:
+        return parked
     return Gradient.apply(x_bin, s_bin, rho, _default_mass(x_bin, mass), snapshot)
 
 
@@ -266,6 +395,9 @@ class DensityGradient(torch.autograd.Function):
 
 
 def density_gradient(x_bin, snapshot, mass=None):
+    parked = _claim(snapshot, "density_gradient", x_bin, mass)
+    if parked is not None:
+        return parked
     return DensityGradient.apply(x_bin, _default_mass(x_bin, mass), snapshot)
 
 
@@ -292,6 +424,11 @@ class MomentMatrix(torch.autograd.Function):
 
 
 def moment_matrix(x_bin, rho, snapshot, mass=None):
+    # the parked matrix carries no autograd history: usable when none is wanted (gradient_hybrid)
+    if not (torch.is_grad_enabled() and (x_bin.requires_grad or rho.requires_grad)):
+        parked = _claim(snapshot, "moment_matrix", x_bin, rho, mass)
+        if parked is not None:
+            return parked
     return MomentMatrix.apply(x_bin, rho, _default_mass(x_bin, mass), snapshot)
 
 

@@ -300,8 +300,9 @@ class _HashGridBase:
 
     # ---- fused sweeps (no counterpart in the reference module) ------------------
     def blur_gradient_forward(self, binned_positions, rho, mass, state_in, state_out, state_gradient_out,
-                              bin_offsets, block_info):
-        """blur and gradient in one launch; ``mass`` and either output may be None."""
+                              bin_offsets, block_info, moment_matrix_out=None):
+        """blur and gradient in one launch; ``mass`` and either output may be None.  With
+        ``moment_matrix_out`` (and both other outputs) the moment matrix rides the same sweep."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
         self._pos(binned_positions, "binned_positions")
         self._bn(rho, "rho")
@@ -313,11 +314,13 @@ class _HashGridBase:
         if state_gradient_out is not None:
             self._bn(state_gradient_out, "state_gradient_out", C, self._dim)
         self._snap(bin_offsets, block_info)
+        if moment_matrix_out is not None:
+            self._bn(moment_matrix_out, "moment_matrix_out", self._dim, self._dim)
         if C == 0:
             return
         self._call(_lib.npa_blur_gradient_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(state_out), N.ptr(state_gradient_out),
-                   N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info))
 
     def blur_gradient_backward(self, binned_positions, rho, mass, state_in, dL_blur_state_out, dL_grad_state_out,
                                grad_x, grad_s, grad_rho, bin_offsets, block_info):
