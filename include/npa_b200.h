@@ -306,6 +306,39 @@ int npa_perception_backward(const npa_grid *g, int32_t channels,
                             const int32_t *bin_offsets, const int32_t *block_info,
                             void *stream);
 
+/* ---- packed perception: the MLP input row of NPA.perceive in two sweeps ------- *
+ * No single counterpart in the reference: replaces the operator calls AND the
+ * torch glue of NPA.perceive (models/npa.py:87-137) with its defaults
+ * state_grad = density_grad = True:
+ *   rho = density(x); blur(x, rho, s); gradient_hybrid(x, rho, s) (sphops/sph.py:474-484,
+ *   value raw @ safe_inv_sym_mat(moment, inv_tol), gradient of the raw operator);
+ *   density_gradient(x); then  z[i] = [ s_i | blur_i | LN(coef * grad_i) | LN(dg_scale * rho_grad_i) ],
+ *   LN(w) = log(1 + |w|) w / |w| when the matching log_norm flag is set, else w.
+ * NPA uses coef = eps / eps0 and dg_scale = coef^(1 + dim) / N.
+ *   z [B,N,2C + C*D + D] out;  rho [B,N], rho_grad [B,N,D] out (needed by backward);
+ *   vgrad [B,N,C,D] out or NULL: the corrected gradient before scaling, needed by backward.
+ * Supports channels <= 128 when channels % 4 == 0 (else <= 32); NPA_ERR_UNSUPPORTED otherwise. */
+int npa_perceive_features_forward(const npa_grid *g, int32_t channels, const float *x_bin,
+                                  const float *mass, const float *s_bin, float coef,
+                                  float dg_scale, float inv_tol, int32_t log_norm_grad,
+                                  int32_t log_norm_dg, float *rho, float *rho_grad, float *z,
+                                  float *vgrad, const int32_t *bin_offsets,
+                                  const int32_t *block_info, void *stream);
+
+/* Backward of the above: dL_dz [B,N,2C+C*D+D] -> grad_s [B,N,C] and, when grad_x != NULL,
+ * grad_x [B,N,P] (through blur, gradient, density and density gradient, as autograd would).
+ * Scratch (caller-allocated, contents undefined): g_blur_scratch [B,N,C], g_grad_scratch
+ * [B,N,C,D]; with grad_x also g_rho_grad_scratch [B,N,D] and grad_rho_scratch [B,N]. */
+int npa_perceive_features_backward(const npa_grid *g, int32_t channels, const float *x_bin,
+                                   const float *mass, const float *s_bin, const float *rho,
+                                   const float *rho_grad, const float *vgrad, const float *dL_dz,
+                                   float coef, float dg_scale, int32_t log_norm_grad,
+                                   int32_t log_norm_dg, float *g_blur_scratch,
+                                   float *g_grad_scratch, float *g_rho_grad_scratch,
+                                   float *grad_rho_scratch, float *grad_x, float *grad_s,
+                                   const int32_t *bin_offsets, const int32_t *block_info,
+                                   void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -171,4 +171,46 @@ __device__ inline float spiky_psi(float d, float h) {
     return 3.0f * t * (h + d) / (d * d * d);
 }
 
+
+// Inverse of a symmetric DxD matrix given by its upper triangle m (row-major order of the
+// triangle), identity when |det| < tol: the rule of the reference's safe_inv_sym_mat
+// (sphops/sph_cuda.cu:3095-3179).  L is the full DxD inverse, row-major.
+template <int D>
+__device__ inline void safe_inverse_sym(const float *m, float tol, float *L) {
+    if (D == 2) {
+        const float det = m[0] * m[2] - m[1] * m[1];
+        if (fabsf(det) < tol) {
+            L[0] = 1.f; L[1] = 0.f; L[2] = 0.f; L[3] = 1.f;
+        } else {
+            const float r = 1.0f / det;
+            L[0] = m[2] * r; L[1] = -m[1] * r; L[2] = -m[1] * r; L[3] = m[0] * r;
+        }
+    } else {
+        const float a = m[0], b = m[1], c = m[2], d = m[3], e = m[4], f = m[5];
+        const float t1 = d * f - e * e, t2 = c * e - b * f, t3 = b * e - c * d;
+        const float det = a * t1 + b * t2 + c * t3;
+        if (fabsf(det) < tol) {
+            L[0] = 1.f; L[1] = 0.f; L[2] = 0.f; L[3] = 0.f; L[4] = 1.f; L[5] = 0.f; L[6] = 0.f; L[7] = 0.f; L[8] = 1.f;
+        } else {
+            const float r = 1.0f / det;
+            const float m01 = t2 * r, m02 = t3 * r, m12 = (b * c - a * e) * r;
+            L[0] = t1 * r; L[1] = m01; L[2] = m02;
+            L[3] = m01; L[4] = (a * f - c * c) * r; L[5] = m12;
+            L[6] = m02; L[7] = m12; L[8] = (a * d - b * b) * r;
+        }
+    }
+}
+
+// w <- log(1 + |w|) * w / max(|w|, 1e-12): the log-normalisation NPA applies to its gradient
+// features (models/npa.py:83-85, torch.nn.functional.normalize's epsilon).
+template <int D>
+__device__ inline void log_normalize(float *w) {
+    float n2 = w[0] * w[0] + w[1] * w[1];
+    if (D == 3) n2 += w[2] * w[2];
+    const float n = sqrtf(n2);
+    const float sc = logf(1.0f + n) / fmaxf(n, 1e-12f);
+#pragma unroll
+    for (int d = 0; d < D; ++d) w[d] *= sc;
+}
+
 }  // namespace npa

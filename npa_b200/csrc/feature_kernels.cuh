@@ -30,6 +30,7 @@ namespace npa {
 constexpr int kListPerWarp = 128;  // accepted-pair slots per warp
 constexpr int kFwdStages = 4;       // pairs fetched ahead per sub-group, forward
 constexpr int kBwdStages = 3;       // same, backward (five pieces per pair)
+constexpr bool kBwdRing = true;     // backward: cp.async ring (true) or register double buffer (false)
 
 template <int VW>
 __device__ inline void load_feat(const float *__restrict__ p, float (&v)[VW]) {
@@ -276,8 +277,51 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 if ((MASK & F_BLUR) && a.blur) store_run<VW, VW>(a.blur + i * C + f0, blur);
                 if ((MASK & F_GRAD) && a.grad) store_run<VW, VW * D>(a.grad + (i * C + f0) * D, gr);
             }
+            if (MASK & F_PACK) {
+                // perception epilogue (the launcher guarantees a single feature chunk): moment matrix ->
+                // safe inverse -> corrected gradient -> scaling and log-normalisation -> packed row
+#pragma unroll
+                for (int q = 0; q < D * (D + 1) / 2; ++q) mom[q] = g.c_g * subgroup_sum<32>(mom[q]);
+                float L[D * D];
+                safe_inverse_sym<D>(mom, a.inv_tol, L);
+                float *zr = a.z + i * a.zstride;
+                if (sg == 0 && fvalid) {
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) {
+                        if (f0 + q < C) {
+                            zr[f0 + q] = si[q];
+                            zr[C + f0 + q] = blur[q];
+                            float v[D];
+#pragma unroll
+                            for (int d = 0; d < D; ++d) {
+                                float acc = 0.f;
+#pragma unroll
+                                for (int kk = 0; kk < D; ++kk) acc = fmaf(gr[q * D + kk], L[kk * D + d], acc);
+                                v[d] = acc;
+                            }
+                            if (a.vgrad) {
+#pragma unroll
+                                for (int d = 0; d < D; ++d) a.vgrad[(i * C + f0 + q) * D + d] = v[d];
+                            }
+#pragma unroll
+                            for (int d = 0; d < D; ++d) v[d] *= a.coef;
+                            if (a.log_norm_grad) log_normalize<D>(v);
+#pragma unroll
+                            for (int d = 0; d < D; ++d) zr[2 * C + (f0 + q) * D + d] = v[d];
+                        }
+                    }
+                }
+                if (lane == 0) {
+                    float w[D];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) w[d] = __ldg(a.rho_grad + i * D + d) * a.dg_scale;
+                    if (a.log_norm_dg) log_normalize<D>(w);
+#pragma unroll
+                    for (int d = 0; d < D; ++d) zr[2 * C + C * D + d] = w[d];
+                }
+            }
         }
-        if (MASK & F_MOMENT) {
+        if ((MASK & F_MOMENT) && !(MASK & F_PACK)) {
 #pragma unroll
             for (int q = 0; q < D * (D + 1) / 2; ++q) mom[q] = g.c_g * subgroup_sum<32>(mom[q]);
             if (lane == 0 && a.moment) {
@@ -364,45 +408,15 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                 }
                 __syncwarp();
                 if (fvalid) {
-                    // stage 3: each sub-group drains every PP-th pair; the neighbour's rows are fetched
-                    // S pairs ahead with cp.async into this lane's ring
-                    auto fetch = [&](int e, int slot) {
-                        if (e < n) {
-                            const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
-                            Piece<VW> *dst = ring + slot * NP * 32;
-                            if (FULL) async_copy<VW * 4>(dst, a.s + row);
-                            if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + row);
-                            if (MASK & F_GRAD) {
-#pragma unroll
-                                for (int d = 0; d < D; ++d)
-                                    async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (row * D + d * VW));
-                            }
-                        }
-                        async_commit();
-                    };
-#pragma unroll
-                    for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
-                    int slot = 0;
-                    for (int e = sg; e < n; e += PP) {
+                    // stage 3: each sub-group drains every PP-th pair.  The neighbour's rows (s_j, dL/dblur_j,
+                    // dL/dgrad_j) are loaded one pair ahead into a second register set (kBwdRing == false)
+                    // or S pairs ahead with cp.async into this lane's shared-memory ring.
+                    auto compute = [&](int e, const float (&sj)[VW], const float (&gbj)[VW], const float (&ggj)[VW * D]) {
                         const float4 e0 = geo[e];
                         const float4 e1 = ker[e];
                         const float vj = vol[e];
                         const float rv[3] = {e0.x, e0.y, e0.z};
-                        async_wait<S - 1>();
-                        const Piece<VW> *src = ring + slot * NP * 32;
-                        float sj[VW];
-                        if (FULL) {
-                            const Piece<VW> t = src[0];
-#pragma unroll
-                            for (int q = 0; q < VW; ++q) sj[q] = t.v[q];
-                        }
                         if (MASK & F_BLUR) {
-                            float gbj[VW];
-                            {
-                                const Piece<VW> t = src[32];
-#pragma unroll
-                                for (int q = 0; q < VW; ++q) gbj[q] = t.v[q];
-                            }
                             float A = 0.f, Bp = 0.f;
 #pragma unroll
                             for (int q = 0; q < VW; ++q) {
@@ -420,13 +434,6 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                             }
                         }
                         if (MASK & F_GRAD) {
-                            float ggj[VW * D];
-#pragma unroll
-                            for (int d = 0; d < D; ++d) {
-                                const Piece<VW> t = src[(2 + d) * 32];
-#pragma unroll
-                                for (int q = 0; q < VW; ++q) ggj[d * VW + q] = t.v[q];
-                            }
                             float kvec[3];
 #pragma unroll
                             for (int d = 0; d < D; ++d) kvec[d] = e1.z * rv[d];
@@ -455,11 +462,73 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                                 for (int d = 0; d < D; ++d) dxg[d] += e1.z * u[d] - sc * rv[d];
                             }
                         }
-                        // refill the slot only after its values were consumed by the arithmetic above
-                        fetch(e + S * PP, slot);
-                        slot = slot + 1 == S ? 0 : slot + 1;
+                    };
+                    if (!kBwdRing) {
+                        auto load = [&](int e, float (&sj)[VW], float (&gbj)[VW], float (&ggj)[VW * D]) {
+                            const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
+                            if (FULL) load_feat<VW>(a.s + row, sj);
+                            if (MASK & F_BLUR) load_feat<VW>(a.g_blur + row, gbj);
+                            if (MASK & F_GRAD) load_run<VW, VW * D>(a.g_grad + row * D, ggj);
+                        };
+                        float sA[VW] = {}, bA[VW] = {}, gA[VW * D] = {}, sB[VW] = {}, bB[VW] = {}, gB[VW * D] = {};
+                        int e = sg;
+                        if (e < n) load(e, sA, bA, gA);
+                        while (e < n) {
+                            if (e + PP < n) load(e + PP, sB, bB, gB);
+                            compute(e, sA, bA, gA);
+                            e += PP;
+                            if (e >= n) break;
+                            if (e + PP < n) load(e + PP, sA, bA, gA);
+                            compute(e, sB, bB, gB);
+                            e += PP;
+                        }
+                    } else {
+                        auto fetch = [&](int e, int slot) {
+                            if (e < n) {
+                                const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
+                                Piece<VW> *dst = ring + slot * NP * 32;
+                                if (FULL) async_copy<VW * 4>(dst, a.s + row);
+                                if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + row);
+                                if (MASK & F_GRAD) {
+#pragma unroll
+                                    for (int d = 0; d < D; ++d)
+                                        async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (row * D + d * VW));
+                                }
+                            }
+                            async_commit();
+                        };
+#pragma unroll
+                        for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
+                        int slot = 0;
+                        for (int e = sg; e < n; e += PP) {
+                            async_wait<S - 1>();
+                            const Piece<VW> *src = ring + slot * NP * 32;
+                            float sj[VW] = {}, gbj[VW] = {}, ggj[VW * D] = {};
+                            if (FULL) {
+                                const Piece<VW> t = src[0];
+#pragma unroll
+                                for (int q = 0; q < VW; ++q) sj[q] = t.v[q];
+                            }
+                            if (MASK & F_BLUR) {
+                                const Piece<VW> t = src[32];
+#pragma unroll
+                                for (int q = 0; q < VW; ++q) gbj[q] = t.v[q];
+                            }
+                            if (MASK & F_GRAD) {
+#pragma unroll
+                                for (int d = 0; d < D; ++d) {
+                                    const Piece<VW> t = src[(2 + d) * 32];
+#pragma unroll
+                                    for (int q = 0; q < VW; ++q) ggj[d * VW + q] = t.v[q];
+                                }
+                            }
+                            compute(e, sj, gbj, ggj);
+                            // refill the slot only after its values were consumed by the arithmetic above
+                            fetch(e + S * PP, slot);
+                            slot = slot + 1 == S ? 0 : slot + 1;
+                        }
+                        async_wait<0>();
                     }
-                    async_wait<0>();
                 }
                 __syncwarp();
             };
@@ -526,6 +595,11 @@ int launch_feature_forward_shape(const Geom &g, int mask, const FeatureFwdArgs &
         case F_BLUR | F_GRAD | F_MOMENT:
             return launch_feature_forward_mask<VW>(
                 g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD | F_MOMENT>, a, st);
+        case F_BLUR | F_GRAD | F_MOMENT | F_PACK:
+            if (a.C > LPP * VW)
+                return fail(NPA_ERR_UNSUPPORTED, "the packed perception sweep supports up to %d features here", LPP * VW);
+            return launch_feature_forward_mask<VW>(
+                g, feature_forward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD | F_MOMENT | F_PACK>, a, st);
         default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported feature forward mask %d", mask);
     }
 }
@@ -546,7 +620,7 @@ int launch_feature_forward_geom(const Geom &g, int mask, const FeatureFwdArgs &a
 template <int D, int VW, typename Kernel>
 int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdArgs &a, cudaStream_t st) {
     const int threads = kWarpsPerCta * 32;
-    const size_t dyn = (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>);
+    const size_t dyn = kBwdRing ? (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>) : 0;
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;

@@ -9,7 +9,9 @@ namespace npa {
 enum { S_COUNT = 1, S_DENSITY = 2, S_DGRAD = 4, S_MOMENT = 8 };
 // Which feature operators a sweep computes.
 // F_MOMENT (forward only) adds the moment matrix to a blur + gradient sweep.
-enum { F_BLUR = 1, F_GRAD = 2, F_MOMENT = 4 };
+// F_PACK (forward only, with all three others) applies the perception epilogue per particle and
+// writes the packed perception vector instead of the separate tensors.
+enum { F_BLUR = 1, F_GRAD = 2, F_MOMENT = 4, F_PACK = 8 };
 
 struct ScalarFwdArgs {
     const float *x;       // [B,N,P] cell order
@@ -49,6 +51,13 @@ struct FeatureFwdArgs {
     const int32_t *bin_offsets;
     const int32_t *block_info;
     float *moment;       // [B,N,D,D], only with F_MOMENT
+    // ---- F_PACK: z[i] = [ s_i | blur_i | lognorm(coef * grad_i @ safe_inv(M_i)) | lognorm(dg_scale * rho_grad_i) ]
+    float *z;                // [B,N,zstride], zstride = 2C + C*D + D
+    int zstride;
+    float *vgrad;            // [B,N,C,D] or NULL: grad_i @ safe_inv(M_i), kept for the backward pass
+    const float *rho_grad;   // [B,N,D] density gradient of the same positions
+    float coef, dg_scale, inv_tol;
+    int log_norm_grad, log_norm_dg;
 };
 
 struct FeatureBwdArgs {

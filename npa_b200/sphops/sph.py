@@ -508,3 +508,67 @@ def perceive(x_bin, s_bin, snapshot, mass=None, with_density_gradient=True):
     if mass is not None:
         mass = _default_mass(x_bin, mass)
     return Perception.apply(x_bin, s_bin, mass, snapshot, with_density_gradient)
+
+
+class PerceiveFeatures(torch.autograd.Function):
+    """The packed perception row of NPA.perceive (models/npa.py:87-137) as one autograd node."""
+
+    @staticmethod
+    def forward(ctx, x_bin, s_bin, mass, snapshot, coef, dg_scale, inv_tol, log_norm_grad, log_norm_dg):
+        B, N, C = s_bin.shape
+        dev, D = x_bin.device, snapshot.dim
+        f32 = dict(dtype=torch.float32, device=dev)
+        rho = torch.empty(B, N, **f32)
+        rho_grad = torch.empty(B, N, D, **f32)
+        z = torch.empty(B, N, 2 * C + C * D + D, **f32)
+        keep = x_bin.requires_grad or s_bin.requires_grad
+        vgrad = torch.empty(B, N, C, D, **f32) if keep else None
+        snapshot.grid.perceive_features_forward(x_bin, mass, s_bin, coef, dg_scale, inv_tol, log_norm_grad,
+                                                log_norm_dg, rho, rho_grad, z, vgrad, snapshot.bin_offsets,
+                                                snapshot.block_info)
+        if keep:
+            ctx.save_for_backward(x_bin, s_bin, rho, rho_grad, vgrad, *([] if mass is None else [mass]))
+        ctx.has_mass = mass is not None
+        ctx.snapshot = snapshot
+        ctx.consts = (coef, dg_scale, log_norm_grad, log_norm_dg)
+        ctx.needs = (x_bin.requires_grad, s_bin.requires_grad)
+        return z
+
+    @staticmethod
+    def backward(ctx, g_z):
+        dLdx, dLds = ctx.needs
+        if not (dLdx or dLds):
+            return (None,) * 9
+        saved = ctx.saved_tensors
+        x_bin, s_bin, rho, rho_grad, vgrad = saved[:5]
+        mass = saved[5] if ctx.has_mass else None
+        coef, dg_scale, ln_g, ln_dg = ctx.consts
+        snap = ctx.snapshot
+        g_blur = torch.empty_like(s_bin)
+        g_grad = torch.empty_like(vgrad)
+        grad_x = torch.empty_like(x_bin) if dLdx else None
+        grad_s = torch.empty_like(s_bin)
+        g_rho_grad = torch.empty_like(rho_grad) if dLdx else None
+        grad_rho = torch.empty_like(rho) if dLdx else None
+        snap.grid.perceive_features_backward(x_bin, mass, s_bin, rho, rho_grad, vgrad, g_z.contiguous(), coef,
+                                             dg_scale, ln_g, ln_dg, g_blur, g_grad, g_rho_grad, grad_rho, grad_x,
+                                             grad_s, snap.bin_offsets, snap.block_info)
+        return (grad_x, grad_s if dLds else None) + (None,) * 7
+
+
+def perceive_features(x_bin, s_bin, snapshot, eps0, mass=None, log_norm_grad=True, log_norm_density_grad=True,
+                      inv_rtol=1e-3):
+    """The perception vector ``z [B, N, 2C + C*dim + dim]`` an NPA model feeds its MLP, in two sweeps.
+
+    Same value and gradients as the body of ``NPA.perceive`` with its defaults (state and density
+    gradients on): ``[s | blur(s) | LN(coef * gradient_hybrid(s)) | LN(coef^(1+dim)/N * density_gradient)]``
+    with ``coef = eps / eps0`` and ``LN(w) = log(1+|w|) w/|w|`` (skipped when the flag is False).
+    Pass ``x_bin.detach()`` to stop gradients into the positions, as NPA does by default.
+    """
+    if mass is not None:
+        mass = _default_mass(x_bin, mass)
+    N = x_bin.shape[1]
+    coef = float(snapshot.grid.eps) / float(eps0)
+    dg_scale = coef ** (1 + snapshot.dim) / N
+    return PerceiveFeatures.apply(x_bin, s_bin, mass, snapshot, coef, dg_scale, float(inv_rtol),
+                                  bool(log_norm_grad), bool(log_norm_density_grad))

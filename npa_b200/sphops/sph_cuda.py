@@ -366,6 +366,57 @@ class _HashGridBase:
                    N.ptr(mass), N.ptr(dL_rho_a), N.ptr(dL_rho_b), N.ptr(dL_density_gradient_out), N.ptr(grad_x),
                    1 if accumulate else 0, N.ptr(bin_offsets), N.ptr(block_info))
 
+    # ---- packed perception (no counterpart in the reference module) ------------
+    def perceive_features_forward(self, binned_positions, mass, state_in, coef, dg_scale, inv_tol, log_norm_grad,
+                                  log_norm_dg, rho, density_gradient_out, z, corrected_gradient_out, bin_offsets,
+                                  block_info):
+        """Two sweeps that write the packed perception row z; ``mass`` and ``corrected_gradient_out`` may be None."""
+        C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
+        D = self._dim
+        self._pos(binned_positions, "binned_positions")
+        self._bn(state_in, "state_in", C)
+        if mass is not None:
+            self._bn(mass, "mass")
+        self._bn(rho, "rho")
+        self._bn(density_gradient_out, "density_gradient_out", D)
+        self._bn(z, "z", 2 * C + C * D + D)
+        if corrected_gradient_out is not None:
+            self._bn(corrected_gradient_out, "corrected_gradient_out", C, D)
+        self._snap(bin_offsets, block_info)
+        self._call(_lib.npa_perceive_features_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
+                   N.ptr(mass), N.ptr(state_in), float(coef), float(dg_scale), float(inv_tol),
+                   1 if log_norm_grad else 0, 1 if log_norm_dg else 0, N.ptr(rho), N.ptr(density_gradient_out),
+                   N.ptr(z), N.ptr(corrected_gradient_out), N.ptr(bin_offsets), N.ptr(block_info))
+
+    def perceive_features_backward(self, binned_positions, mass, state_in, rho, density_gradient, corrected_gradient,
+                                   dL_dz, coef, dg_scale, log_norm_grad, log_norm_dg, g_blur_scratch, g_grad_scratch,
+                                   g_rho_grad_scratch, grad_rho_scratch, grad_x, grad_s, bin_offsets, block_info):
+        """Backward of ``perceive_features_forward``; ``grad_x`` (and its two scratch tensors) may be None."""
+        C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
+        D = self._dim
+        self._pos(binned_positions, "binned_positions")
+        self._bn(state_in, "state_in", C)
+        if mass is not None:
+            self._bn(mass, "mass")
+        self._bn(rho, "rho")
+        self._bn(density_gradient, "density_gradient", D)
+        self._bn(corrected_gradient, "corrected_gradient", C, D)
+        self._bn(dL_dz, "dL_dz", 2 * C + C * D + D)
+        self._bn(g_blur_scratch, "g_blur_scratch", C)
+        self._bn(g_grad_scratch, "g_grad_scratch", C, D)
+        if grad_x is not None:
+            self._pos(grad_x, "grad_x")
+            self._bn(g_rho_grad_scratch, "g_rho_grad_scratch", D)
+            self._bn(grad_rho_scratch, "grad_rho_scratch")
+        if grad_s is not None:
+            self._bn(grad_s, "grad_s", C)
+        self._snap(bin_offsets, block_info)
+        self._call(_lib.npa_perceive_features_backward, binned_positions, self._ref(), C, N.ptr(binned_positions),
+                   N.ptr(mass), N.ptr(state_in), N.ptr(rho), N.ptr(density_gradient), N.ptr(corrected_gradient),
+                   N.ptr(dL_dz), float(coef), float(dg_scale), 1 if log_norm_grad else 0, 1 if log_norm_dg else 0,
+                   N.ptr(g_blur_scratch), N.ptr(g_grad_scratch), N.ptr(g_rho_grad_scratch), N.ptr(grad_rho_scratch),
+                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(bin_offsets), N.ptr(block_info))
+
     # ---- fused perception (no counterpart in the reference module) -------------
     def perception_forward(self, binned_positions, mass, state_in, rho, count, density_gradient_out,
                            state_out, state_gradient_out, moment_matrix_out, bin_offsets, block_info):

@@ -127,3 +127,56 @@ def test_fused_moment_equals_single_operator():
         assert torch.equal(grad, sph.gradient(xb, rho, sb, snap))
         ref = sph.moment_matrix(xb, rho, snap)
         assert torch.allclose(mom, ref, rtol=1e-5, atol=1e-6 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("dim,boundary,C,stopgrad,log_norm", [
+    (3, "clamped", 16, True, True), (3, "clamped", 32, False, True), (2, "periodic", 16, True, True),
+    (2, "clamped", 6, False, True), (2, "clamped", 16, False, False), (3, "periodic", 5, True, True)])
+def test_packed_perception_equals_the_operator_sequence(dim, boundary, C, stopgrad, log_norm):
+    """perceive_features (two sweeps + fused epilogue) against the per-operator calls + torch glue."""
+    from npa_b200 import sphops as sph
+    sph.enable_fusion(False)
+    w = Workload("pack", dim=dim, B=2, N=2500, C=C, eps=0.12 if dim == 3 else 0.05,
+                 grid_size=(10, 10, 10) if dim == 3 else (20, 20), boundary=boundary)
+    x, s, _ = make_inputs(w, seed=11)
+    x[..., :dim] *= 0.95 * w.grid_size[0] * w.eps
+    x[:, 7] = x[:, 6]                       # a coincident pair
+    x[:, -1, :dim] = 0.49 * w.grid_size[0] * w.eps   # an isolated particle: singular moment matrix -> identity
+    grid = make_grid(sph, w)
+    eps0 = 0.07
+    up = torch.randn(w.B, w.N, 2 * C + C * dim + dim, generator=torch.Generator().manual_seed(2)).cuda()
+
+    def reference(xr, sr):
+        snap = grid.instantiate(xr.detach())
+        x_bin, s_bin = sph.bin_particles(xr, sr, snap)
+        xp = x_bin.detach() if stopgrad else x_bin
+        rho = sph.density(xp, snap)
+        blur_s = sph.blur(xp, rho, s_bin, snap)
+        g = sph.gradient_hybrid(xp, rho, s_bin, snap) * (grid.eps / eps0)
+        dg = sph.density_gradient(xp, snap) * ((grid.eps / eps0) ** (1 + dim)) / w.N
+        if log_norm:
+            g, dg = _log_normalize(g), _log_normalize(dg)
+        return torch.cat([s_bin, blur_s, g.view(w.B, w.N, -1), dg], dim=-1)
+
+    def packed(xr, sr):
+        snap = grid.instantiate(xr.detach())
+        x_bin, s_bin = sph.bin_particles(xr, sr, snap)
+        xp = x_bin.detach() if stopgrad else x_bin
+        return sph.perceive_features(xp, s_bin, snap, eps0, log_norm_grad=log_norm, log_norm_density_grad=log_norm)
+
+    outs = []
+    for fn in (reference, packed):
+        xr, sr = x.cuda().requires_grad_(True), s.cuda().requires_grad_(True)
+        z = fn(xr, sr)
+        z.backward(up)
+        outs.append((z.detach(), sr.grad, xr.grad))
+    (zr, gsr, gxr), (zp, gsp, gxp) = outs
+    assert zp.shape == zr.shape
+    assert torch.allclose(zp, zr, rtol=1e-4, atol=1e-5 * float(zr.abs().max()))
+    assert torch.allclose(gsp, gsr, rtol=1e-4, atol=1e-5 * float(gsr.abs().max()))
+    if stopgrad:
+        assert gxp is None or float(gxp.abs().max()) == 0.0
+    else:
+        assert torch.allclose(gxp, gxr, rtol=1e-4, atol=2e-5 * float(gxr.abs().max()))
+    with torch.no_grad():                   # inference path keeps no tensor for backward
+        assert torch.equal(packed(x.cuda(), s.cuda()), zp)
