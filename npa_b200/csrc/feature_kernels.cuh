@@ -284,32 +284,35 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 for (int q = 0; q < D * (D + 1) / 2; ++q) mom[q] = g.c_g * subgroup_sum<32>(mom[q]);
                 float L[D * D];
                 safe_inverse_sym<D>(mom, a.inv_tol, L);
+                // the row is assembled in the (now idle) pair list of this warp and written coalesced
                 float *zr = a.z + i * a.zstride;
+                const bool staged = a.zstride <= kListPerWarp * 4;
+                float *zs = staged ? reinterpret_cast<float *>(ent) : zr;
+                __syncwarp();
                 if (sg == 0 && fvalid) {
+                    float vall[VW * D];
 #pragma unroll
                     for (int q = 0; q < VW; ++q) {
+                        float v[D];
+#pragma unroll
+                        for (int d = 0; d < D; ++d) {
+                            float acc = 0.f;
+#pragma unroll
+                            for (int kk = 0; kk < D; ++kk) acc = fmaf(gr[q * D + kk], L[kk * D + d], acc);
+                            v[d] = acc;
+                            vall[q * D + d] = acc;
+                        }
                         if (f0 + q < C) {
-                            zr[f0 + q] = si[q];
-                            zr[C + f0 + q] = blur[q];
-                            float v[D];
-#pragma unroll
-                            for (int d = 0; d < D; ++d) {
-                                float acc = 0.f;
-#pragma unroll
-                                for (int kk = 0; kk < D; ++kk) acc = fmaf(gr[q * D + kk], L[kk * D + d], acc);
-                                v[d] = acc;
-                            }
-                            if (a.vgrad) {
-#pragma unroll
-                                for (int d = 0; d < D; ++d) a.vgrad[(i * C + f0 + q) * D + d] = v[d];
-                            }
+                            zs[f0 + q] = si[q];
+                            zs[C + f0 + q] = blur[q];
 #pragma unroll
                             for (int d = 0; d < D; ++d) v[d] *= a.coef;
                             if (a.log_norm_grad) log_normalize<D>(v);
 #pragma unroll
-                            for (int d = 0; d < D; ++d) zr[2 * C + (f0 + q) * D + d] = v[d];
+                            for (int d = 0; d < D; ++d) zs[2 * C + (f0 + q) * D + d] = v[d];
                         }
                     }
+                    if (a.vgrad) store_run<VW, VW * D>(a.vgrad + (i * C + f0) * D, vall);
                 }
                 if (lane == 0) {
                     float w[D];
@@ -317,7 +320,12 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     for (int d = 0; d < D; ++d) w[d] = __ldg(a.rho_grad + i * D + d) * a.dg_scale;
                     if (a.log_norm_dg) log_normalize<D>(w);
 #pragma unroll
-                    for (int d = 0; d < D; ++d) zr[2 * C + C * D + d] = w[d];
+                    for (int d = 0; d < D; ++d) zs[2 * C + C * D + d] = w[d];
+                }
+                if (staged) {
+                    __syncwarp();
+                    for (int c = lane; c < a.zstride; c += 32) zr[c] = zs[c];
+                    __syncwarp();
                 }
             }
         }
@@ -463,7 +471,8 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                             }
                         }
                     };
-                    if (!kBwdRing) {
+                    if (!(kBwdRing && FULL)) {  // the features-only pass has registers to spare
+
                         auto load = [&](int e, float (&sj)[VW], float (&gbj)[VW], float (&ggj)[VW * D]) {
                             const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
                             if (FULL) load_feat<VW>(a.s + row, sj);
@@ -617,10 +626,10 @@ int launch_feature_forward_geom(const Geom &g, int mask, const FeatureFwdArgs &a
     return launch_feature_forward_shape<D, PER, 32, 1>(g, mask, a, st);
 }
 
-template <int D, int VW, typename Kernel>
+template <int D, int VW, bool FULL, typename Kernel>
 int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdArgs &a, cudaStream_t st) {
     const int threads = kWarpsPerCta * 32;
-    const size_t dyn = kBwdRing ? (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>) : 0;
+    const size_t dyn = (kBwdRing && FULL) ? (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>) : 0;
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
@@ -633,11 +642,11 @@ template <int D, bool PER, int LPP, int VW, bool FULL>
 int launch_feature_backward_shape(const Geom &g, int mask, const FeatureBwdArgs &a, cudaStream_t st) {
     switch (mask) {
         case F_BLUR:
-            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR, FULL>, a, st);
+            return launch_feature_backward_mask<D, VW, FULL>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR, FULL>, a, st);
         case F_GRAD:
-            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_GRAD, FULL>, a, st);
+            return launch_feature_backward_mask<D, VW, FULL>(g, feature_backward_kernel<D, PER, LPP, VW, F_GRAD, FULL>, a, st);
         case F_BLUR | F_GRAD:
-            return launch_feature_backward_mask<D, VW>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD, FULL>, a, st);
+            return launch_feature_backward_mask<D, VW, FULL>(g, feature_backward_kernel<D, PER, LPP, VW, F_BLUR | F_GRAD, FULL>, a, st);
         default: return fail(NPA_ERR_INVALID_ARGUMENT, "unsupported feature backward mask %d", mask);
     }
 }

@@ -122,7 +122,8 @@ def run_case(ts, cfg, seed, dtype):
 
 
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    # default: a sibling directory "reference" of this repository
+    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE.parents[2] / "reference"
     ts = load_torch_sph(ref_root)
     torch.set_num_threads(8)
     for idx, (name, cfg) in enumerate(CASES.items()):

@@ -2,6 +2,7 @@
 geometry validation, and the Python surface the reference's callers rely on.  No kernel is launched."""
 import ast
 import ctypes
+import os
 import re
 from pathlib import Path
 
@@ -10,7 +11,8 @@ import torch
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = ROOT / "include" / "npa_b200.h"
-REFERENCE = Path("/root/reference")
+# the reference checkout, when present: $NPA_REFERENCE_ROOT or a sibling directory "reference" of this repository
+REFERENCE = Path(os.environ.get("NPA_REFERENCE_ROOT", ROOT.parent / "reference"))
 
 
 def _declared_symbols():
