@@ -289,30 +289,45 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 const bool staged = a.zstride <= kListPerWarp * 4;
                 float *zs = staged ? reinterpret_cast<float *>(ent) : zr;
                 __syncwarp();
-                if (sg == 0 && fvalid) {
-                    float vall[VW * D];
+                // after the butterfly every sub-group holds the full sums: sub-group sg finishes the
+                // features q = sg, sg + PP, ... of its lanes, so the epilogue arithmetic is spread over the warp
+#pragma unroll
+                for (int t = 0; t < (VW + PP - 1) / PP; ++t) {
+                    const int qsel = t * PP + sg;
+                    float gsel[D], ssel = 0.f, bsel = 0.f;
+#pragma unroll
+                    for (int d = 0; d < D; ++d) gsel[d] = 0.f;
 #pragma unroll
                     for (int q = 0; q < VW; ++q) {
-                        float v[D];
+                        if (q == qsel) {
+                            ssel = si[q];
+                            bsel = blur[q];
 #pragma unroll
-                        for (int d = 0; d < D; ++d) {
-                            float acc = 0.f;
-#pragma unroll
-                            for (int kk = 0; kk < D; ++kk) acc = fmaf(gr[q * D + kk], L[kk * D + d], acc);
-                            v[d] = acc;
-                            vall[q * D + d] = acc;
-                        }
-                        if (f0 + q < C) {
-                            zs[f0 + q] = si[q];
-                            zs[C + f0 + q] = blur[q];
-#pragma unroll
-                            for (int d = 0; d < D; ++d) v[d] *= a.coef;
-                            if (a.log_norm_grad) log_normalize<D>(v);
-#pragma unroll
-                            for (int d = 0; d < D; ++d) zs[2 * C + (f0 + q) * D + d] = v[d];
+                            for (int d = 0; d < D; ++d) gsel[d] = gr[q * D + d];
                         }
                     }
-                    if (a.vgrad) store_run<VW, VW * D>(a.vgrad + (i * C + f0) * D, vall);
+                    float v[D];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int kk = 0; kk < D; ++kk) acc = fmaf(gsel[kk], L[kk * D + d], acc);
+                        v[d] = acc;
+                    }
+                    const int f = f0 + qsel;
+                    if (fvalid && qsel < VW && f < C) {
+                        zs[f] = ssel;
+                        zs[C + f] = bsel;
+                        if (a.vgrad) {
+#pragma unroll
+                            for (int d = 0; d < D; ++d) a.vgrad[(i * C + f) * D + d] = v[d];
+                        }
+#pragma unroll
+                        for (int d = 0; d < D; ++d) v[d] *= a.coef;
+                        if (a.log_norm_grad) log_normalize<D>(v);
+#pragma unroll
+                        for (int d = 0; d < D; ++d) zs[2 * C + f * D + d] = v[d];
+                    }
                 }
                 if (lane == 0) {
                     float w[D];
@@ -348,7 +363,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
 }
 
 template <int D, bool PER, int LPP, int VW, int MASK, bool FULL>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, FULL ? 2 : 3)
 feature_backward_kernel(FeatureBwdArgs a, Geom g) {
     constexpr int PP = 32 / LPP;
     __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
@@ -387,6 +402,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             const int f0 = fbase + sl * VW;
             const bool fvalid = f0 < C;
             float si[VW], gbi[VW], ggi[VW * D], ds[VW], dsg[VW];
+            float tsum[3] = {0.f, 0.f, 0.f};  // features-only pass: sum_j v_j K_j (identical in every lane)
 #pragma unroll
             for (int q = 0; q < VW; ++q) { si[q] = 0.f; gbi[q] = 0.f; ds[q] = 0.f; dsg[q] = 0.f; }
 #pragma unroll
@@ -394,7 +410,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             if (fvalid) {
                 if (FULL) load_feat<VW>(a.s + i * C + f0, si);
                 if (FULL && (MASK & F_BLUR)) load_feat<VW>(a.g_blur + i * C + f0, gbi);
-                if (MASK & F_GRAD) load_run<VW, VW * D>(a.g_grad + (i * C + f0) * D, ggi);
+                if (FULL && (MASK & F_GRAD)) load_run<VW, VW * D>(a.g_grad + (i * C + f0) * D, ggi);
             }
 
             auto flush = [&](int n) {
@@ -441,7 +457,17 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                                 drs = fmaf(e1.x, Bp, drs);
                             }
                         }
-                        if (MASK & F_GRAD) {
+                        if ((MASK & F_GRAD) && !FULL) {
+                            // ds_i[f] = -cg ( gG_i[f] . T + v_i sum_j K_j . gG_j[f] ),  T = sum_j v_j K_j
+#pragma unroll
+                            for (int d = 0; d < D; ++d) {
+                                const float kd = e1.z * rv[d];
+                                tsum[d] = fmaf(vj, kd, tsum[d]);
+#pragma unroll
+                                for (int q = 0; q < VW; ++q) dsg[q] = fmaf(kd, ggj[q * D + d], dsg[q]);
+                            }
+                        }
+                        if ((MASK & F_GRAD) && FULL) {
                             float kvec[3];
 #pragma unroll
                             for (int d = 0; d < D; ++d) kvec[d] = e1.z * rv[d];
@@ -545,9 +571,23 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
 
             if (a.grad_s) {
                 float out[VW];
+                if (FULL) {
 #pragma unroll
-                for (int q = 0; q < VW; ++q)
-                    out[q] = across_subgroups<LPP>(g.c_s * vi * ds[q] - g.c_g * dsg[q]);
+                    for (int q = 0; q < VW; ++q)
+                        out[q] = across_subgroups<LPP>(g.c_s * vi * ds[q] - g.c_g * dsg[q]);
+                } else {
+                    // each sub-group saw every PP-th pair: combine, then add the i-side term once
+#pragma unroll
+                    for (int d = 0; d < D; ++d) tsum[d] = across_subgroups<LPP>(tsum[d]);
+                    if (fvalid && (MASK & F_GRAD)) load_run<VW, VW * D>(a.g_grad + (i * C + f0) * D, ggi);
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) {
+                        float own = 0.f;
+#pragma unroll
+                        for (int d = 0; d < D; ++d) own = fmaf(ggi[q * D + d], tsum[d], own);
+                        out[q] = across_subgroups<LPP>(vi * (g.c_s * ds[q] - g.c_g * dsg[q])) - g.c_g * own;
+                    }
+                }
                 if (sg == 0 && fvalid) store_run<VW, VW>(a.grad_s + i * C + f0, out);
             }
         }
