@@ -296,30 +296,29 @@ def run_gpu_arm(args, w):
     value = world * B * N / (step_ms * 1e-3)
 
     # ---- end to end through the public API from pinned host buffers --------------------------
-    gx_h = torch.empty_like(x_h).pin_memory()
-    gs_h = torch.empty_like(s_h).pin_memory()
+    # Every step copies positions and features host -> device, runs binning + forward + backward
+    # through the public sphops API and copies both gradients device -> host.  The three stages of
+    # consecutive steps overlap on three streams (npa_b200.pipeline), as a host-fed loop would run.
+    from npa_b200.pipeline import HostStepPipeline
 
-    def e2e_step():
-        xi = torch.empty_like(x_d).copy_(x_h, non_blocking=True).requires_grad_(True)
-        si = torch.empty_like(s_d).copy_(s_h, non_blocking=True).requires_grad_(True)
+    def api_step(inp):
+        xi, si = inp[0].detach().requires_grad_(True), inp[1].detach().requires_grad_(True)
         snap = grid.instantiate(xi.detach())
         xb, sb = sph.bin_particles(xi, si, snap)
         r, bl, gr = sph.perceive(xb, sb, snap, with_density_gradient=False)
         torch.autograd.backward([r, bl, gr], [ups["g_rho"], ups["g_blur"], ups["g_grad"]])
-        gx_h.copy_(xi.grad, non_blocking=True)
-        gs_h.copy_(si.grad, non_blocking=True)
         if world > 1:
             dist.all_reduce(mlp_grad)
+        return xi.grad, si.grad
 
-    for _ in range(3):
-        e2e_step()
+    pipe = HostStepPipeline(api_step, (x_h, s_h), (x_h, s_h), device=dev, depth=2)
+    pipe.run([(x_h, s_h)] * 3)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    pipe.run([(x_h, s_h)] * args.steps)   # returns once the last gradients are in host memory
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
@@ -327,7 +326,7 @@ def run_gpu_arm(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
     h2d = x_h.numel() * 4 + s_h.numel() * 4
-    d2h = gx_h.numel() * 4 + gs_h.numel() * 4
+    d2h = h2d
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
