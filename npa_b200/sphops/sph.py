@@ -567,8 +567,24 @@ def perceive_features(x_bin, s_bin, snapshot, eps0, mass=None, log_norm_grad=Tru
     """
     if mass is not None:
         mass = _default_mass(x_bin, mass)
-    N = x_bin.shape[1]
+    B, N, C = s_bin.shape
     coef = float(snapshot.grid.eps) / float(eps0)
     dg_scale = coef ** (1 + snapshot.dim) / N
+    if not ((C % 4 == 0 and C <= 128) or C <= 32):
+        # wider feature rows than one warp pass covers: same result from the separate operators
+        def _ln(v):
+            return torch.log(1.0 + v.norm(dim=-1, keepdim=True)) * torch.nn.functional.normalize(v, dim=-1)
+        rho = density(x_bin, snapshot, mass)
+        s_blur = blur(x_bin, rho, s_bin, snapshot, mass)
+        with torch.no_grad():
+            L = safe_inv_sym_mat(moment_matrix(x_bin, rho, snapshot, mass), rtol=inv_rtol)
+        raw = gradient(x_bin, rho, s_bin, snapshot, mass)
+        g = (raw + (raw @ L - raw).detach()) * coef
+        dg = density_gradient(x_bin, snapshot, mass) * dg_scale
+        if log_norm_grad:
+            g = _ln(g)
+        if log_norm_density_grad:
+            dg = _ln(dg)
+        return torch.cat([s_bin, s_blur, g.reshape(B, N, -1), dg], dim=-1)
     return PerceiveFeatures.apply(x_bin, s_bin, mass, snapshot, coef, dg_scale, float(inv_rtol),
                                   bool(log_norm_grad), bool(log_norm_density_grad))

@@ -131,7 +131,8 @@ def test_fused_moment_equals_single_operator():
 
 @pytest.mark.parametrize("dim,boundary,C,stopgrad,log_norm", [
     (3, "clamped", 16, True, True), (3, "clamped", 32, False, True), (2, "periodic", 16, True, True),
-    (2, "clamped", 6, False, True), (2, "clamped", 16, False, False), (3, "periodic", 5, True, True)])
+    (2, "clamped", 6, False, True), (2, "clamped", 16, False, False), (3, "periodic", 5, True, True),
+    (2, "clamped", 64, False, True), (2, "clamped", 132, True, True)])
 def test_packed_perception_equals_the_operator_sequence(dim, boundary, C, stopgrad, log_norm):
     """perceive_features (two sweeps + fused epilogue) against the per-operator calls + torch glue."""
     from npa_b200 import sphops as sph
