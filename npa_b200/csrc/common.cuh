@@ -24,6 +24,7 @@ struct Geom {
     int cells;      // per system
     int B, N, mpb;
     int max_blocks;
+    int split;      // warps sharing one work item in the feature kernels (small problems only)
     float inv_eps;  // 1.0f / float(eps): the multiplier pos2cell uses
     float h;        // float(eps)
     float h2;       // float(eps * eps) rounded once from double, as torch does

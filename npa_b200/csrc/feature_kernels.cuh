@@ -173,13 +173,17 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     const int C = a.C;
 
     // persistent warps: consecutive rows go to the warps of one CTA, then to the next CTA
-    for (int row = blockIdx.x * kWarpsPerCta + warp; row < g.max_blocks; row += gridDim.x * kWarpsPerCta) {
+    // g.split warps share one row (its particles are dealt round-robin) when rows are scarce
+    const int vrows = g.max_blocks * g.split;
+    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    const int row = vrow / g.split, part = vrow - row * g.split;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) break;  // rows after the last work item are zero
+    if (part >= it.count) continue;
     __syncwarp();
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
 
-    for (int k = 0; k < it.count; ++k) {
+    for (int k = part; k < it.count; k += g.split) {
         const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
         float mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // F_MOMENT: upper triangle, lane-partial over pairs
@@ -384,13 +388,17 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
     Piece<VW> *ring = reinterpret_cast<Piece<VW> *>(s_dyn) + (size_t)warp * S * NP * 32 + lane;
     const int C = a.C;
 
-    for (int row = blockIdx.x * kWarpsPerCta + warp; row < g.max_blocks; row += gridDim.x * kWarpsPerCta) {
+    // g.split warps share one row (its particles are dealt round-robin) when rows are scarce
+    const int vrows = g.max_blocks * g.split;
+    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    const int row = vrow / g.split, part = vrow - row * g.split;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) break;  // rows after the last work item are zero
+    if (part >= it.count) continue;
     __syncwarp();
     const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
 
-    for (int k = 0; k < it.count; ++k) {
+    for (int k = part; k < it.count; k += g.split) {
         const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
         const float mi = a.mass ? __ldg(a.mass + i) : 1.0f;
@@ -627,7 +635,7 @@ int launch_feature_forward_mask(const Geom &g, Kernel kernel, const FeatureFwdAr
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
-    const int needed = (g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
     kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
     return check_launch("feature_forward_kernel");
 }
@@ -673,7 +681,7 @@ int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdA
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
-    const int needed = (g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
     kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
     return check_launch("feature_backward_kernel");
 }

@@ -90,6 +90,13 @@ int make_geom(const npa_grid *in, Geom *out) {
     if (max_blocks >= (1ll << 29))
         return fail(NPA_ERR_INVALID_ARGUMENT, "work list of %lld rows is too large", max_blocks);
     g.max_blocks = (int)max_blocks;
+    // Small problems have fewer work items than a B200 has warp slots (148 SMs x ~24 warps); the
+    // feature kernels then let up to 8 warps share the particles of one item.
+    {
+        long long items = (long long)in->batch * (cells < in->particles ? cells : in->particles);
+        long long split = (2ll * 148 * 24) / (items > 0 ? items : 1);
+        g.split = (int)(split < 1 ? 1 : (split > 8 ? 8 : split));
+    }
 
     const float eps_f = (float)in->eps;
     g.h = eps_f;
