@@ -29,7 +29,11 @@ namespace npa {
 
 constexpr int kListPerWarp = 128;  // accepted-pair slots per warp
 constexpr int kFwdStages = 4;       // pairs fetched ahead per sub-group, forward
-constexpr int kBwdStages = 3;       // same, backward (five pieces per pair)
+constexpr int kBwdStages = 2;       // same, backward (five pieces per pair)
+// Full backward: smaller CTAs give the register allocator a finer occupancy grid (5 x 4 warps)
+constexpr int kBwdFullWarps = 4;
+constexpr int kBwdFullCtas = 5;
+constexpr int bwd_warps(bool full) { return full ? kBwdFullWarps : kWarpsPerCta; }
 constexpr bool kBwdRing = true;     // backward: cp.async ring (true) or register double buffer (false)
 
 template <int VW>
@@ -367,13 +371,14 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
 }
 
 template <int D, bool PER, int LPP, int VW, int MASK, bool FULL>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, FULL ? 2 : 3)
+__global__ void __launch_bounds__(bwd_warps(FULL) * 32, FULL ? kBwdFullCtas : 3)
 feature_backward_kernel(FeatureBwdArgs a, Geom g) {
     constexpr int PP = 32 / LPP;
-    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
-    __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z, index of j
-    __shared__ float4 s_ker[kWarpsPerCta][kListPerWarp];  // W, 6(h^2-q)^2, phi, psi
-    __shared__ float s_vol[kWarpsPerCta][kListPerWarp];   // v_j = m_j / rho_j
+    constexpr int WB = bwd_warps(FULL);  // warps per CTA
+    __shared__ int4 s_ranges[WB][kMaxRanges];
+    __shared__ float4 s_geo[WB][kListPerWarp];  // r.x r.y r.z, index of j
+    __shared__ float4 s_ker[WB][kListPerWarp];  // W, 6(h^2-q)^2, phi, psi
+    __shared__ float s_vol[WB][kListPerWarp];   // v_j = m_j / rho_j
     extern __shared__ __align__(16) unsigned char s_dyn[];
     constexpr int S = kBwdStages;
     constexpr int NP = 2 + D;  // pieces per pair and lane: s_j, dL/dblur_j, D pieces of dL/dgrad_j
@@ -390,7 +395,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
 
     // g.split warps share one row (its particles are dealt round-robin) when rows are scarce
     const int vrows = g.max_blocks * g.split;
-    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    for (int vrow = blockIdx.x * WB + warp; vrow < vrows; vrow += gridDim.x * WB) {
     const int row = vrow / g.split, part = vrow - row * g.split;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) break;  // rows after the last work item are zero
@@ -676,12 +681,13 @@ int launch_feature_forward_geom(const Geom &g, int mask, const FeatureFwdArgs &a
 
 template <int D, int VW, bool FULL, typename Kernel>
 int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdArgs &a, cudaStream_t st) {
-    const int threads = kWarpsPerCta * 32;
-    const size_t dyn = (kBwdRing && FULL) ? (size_t)kWarpsPerCta * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>) : 0;
+    constexpr int WB = bwd_warps(FULL);
+    const int threads = WB * 32;
+    const size_t dyn = (kBwdRing && FULL) ? (size_t)WB * kBwdStages * (2 + D) * 32 * sizeof(Piece<VW>) : 0;
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
-    const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int needed = (g.max_blocks * g.split + WB - 1) / WB;
     kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
     return check_launch("feature_backward_kernel");
 }
