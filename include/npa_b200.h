@@ -232,6 +232,16 @@ int npa_moment_matrix_backward(const npa_grid *g, const float *x_bin,
 int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
                          float tol, void *stream);
 
+/* ---- neighbour list cache ---------------------------------------------------- *
+ * Forward and backward of one snapshot visit the same pairs.  The fused entry
+ * points below take an optional cache  pair_cache [B*N, pair_stride] (int32,
+ * caller-allocated; NULL = off): the forward blur/gradient sweep records, per
+ * particle, the number of accepted neighbours and their indices (row = count,
+ * j_0, j_1, ...; count = -1 when there are more than pair_stride - 1), and the
+ * backward sweep given the same cache rebuilds the displacements from the list
+ * instead of testing the ~3^D cells of candidates again (particles marked -1 are
+ * searched as usual).  pair_stride <= 129.  No counterpart in the reference.   */
+
 /* ---- blur + gradient in one launch ------------------------------------------ *
  * The two feature operators share every pair test and every neighbour feature
  * load, so one sweep produces both.  Results equal npa_blur_* / npa_gradient_*
@@ -243,7 +253,7 @@ int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
 int npa_blur_gradient_forward(const npa_grid *g, int32_t channels, const float *x_bin,
                               const float *rho, const float *mass, const float *s_bin,
                               float *s_blur, float *s_grad, float *moment,
-                              const int32_t *bin_offsets, const int32_t *block_info, void *stream);
+                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 /* grad_x == NULL and grad_rho == NULL selects the variant that differentiates
  * with respect to s only. */
@@ -251,7 +261,7 @@ int npa_blur_gradient_backward(const npa_grid *g, int32_t channels, const float 
                                const float *rho, const float *mass, const float *s_bin,
                                const float *dL_dblur, const float *dL_dgrad, float *grad_x,
                                float *grad_s, float *grad_rho, const int32_t *bin_offsets,
-                               const int32_t *block_info, void *stream);
+                               const int32_t *block_info, const int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 /* ---- density + density gradient backward in one launch ---------------------- *
  * Gradient with respect to the positions of  rho = density(x)  and
@@ -284,7 +294,7 @@ int npa_perception_forward(const npa_grid *g, int32_t channels,
                            const float *s_bin, float *rho, float *count,
                            float *rho_grad, float *s_blur, float *s_grad,
                            float *moment, const int32_t *bin_offsets,
-                           const int32_t *block_info, void *stream);
+                           const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 /*
  * Backward of  rho = density(x); blur(x, rho, s); gradient(x, rho, s);
@@ -304,7 +314,7 @@ int npa_perception_backward(const npa_grid *g, int32_t channels,
                             const float *dL_dgrad, const float *dL_drho_grad,
                             float *grad_x, float *grad_s, float *grad_rho_scratch,
                             const int32_t *bin_offsets, const int32_t *block_info,
-                            void *stream);
+                            const int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 /* ---- packed perception: the MLP input row of NPA.perceive in two sweeps ------- *
  * No single counterpart in the reference: replaces the operator calls AND the
@@ -323,7 +333,7 @@ int npa_perceive_features_forward(const npa_grid *g, int32_t channels, const flo
                                   float dg_scale, float inv_tol, int32_t log_norm_grad,
                                   int32_t log_norm_dg, float *rho, float *rho_grad, float *z,
                                   float *vgrad, const int32_t *bin_offsets,
-                                  const int32_t *block_info, void *stream);
+                                  const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 /* Backward of the above: dL_dz [B,N,2C+C*D+D] -> grad_s [B,N,C] and, when grad_x != NULL,
  * grad_x [B,N,P] (through blur, gradient, density and density gradient, as autograd would).
@@ -337,7 +347,7 @@ int npa_perceive_features_backward(const npa_grid *g, int32_t channels, const fl
                                    float *g_grad_scratch, float *g_rho_grad_scratch,
                                    float *grad_rho_scratch, float *grad_x, float *grad_s,
                                    const int32_t *bin_offsets, const int32_t *block_info,
-                                   void *stream);
+                                   const int32_t *pair_cache, int32_t pair_stride, void *stream);
 
 #ifdef __cplusplus
 }

@@ -74,6 +74,12 @@ static int check_channels(const char *name, int C) {
     return NPA_OK;
 }
 
+static int check_pair_cache(const char *name, const void *cache, int stride) {
+    if (cache && (stride < 2 || stride > 129))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "%s: pair_stride must be in [2, 129], got %d", name, stride);
+    return NPA_OK;
+}
+
 static int check_grad_x(const char *name, const Geom &g, const float *grad_x) {
     if (grad_x && (uintptr_t)grad_x % (g.dim == 2 ? 8 : 16))
         return fail(NPA_ERR_INVALID_ARGUMENT, "%s: grad_x must be aligned to one position", name);
@@ -236,7 +242,7 @@ int npa_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_b
 
 int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
                               const float *mass, const float *s_bin, float *s_blur, float *s_grad, float *moment,
-                              const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = begin_op("blur_gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -250,14 +256,17 @@ int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float 
         mask |= F_MOMENT;
     }
     if (!mask) return NPA_OK;
+    if ((rc = check_pair_cache("blur_gradient_forward", pair_cache, pair_stride)) != NPA_OK) return rc;
     FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info, moment};
+    a.pair_cache = pair_cache;
+    a.pair_stride = pair_stride;
     return launch_feature_forward(g, mask, a, (cudaStream_t)stream);
 }
 
 int npa_blur_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
                                const float *mass, const float *s_bin, const float *dL_dblur,
                                const float *dL_dgrad, float *grad_x, float *grad_s, float *grad_rho,
-                               const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+                               const int32_t *bin_offsets, const int32_t *block_info, const int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = begin_op("blur_gradient_backward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -268,7 +277,9 @@ int npa_blur_gradient_backward(const npa_grid *gd, int32_t channels, const float
     if ((rc = check_grad_x("blur_gradient_backward", g, grad_x)) != NPA_OK) return rc;
     const int mask = (dL_dblur ? F_BLUR : 0) | (dL_dgrad ? F_GRAD : 0);
     if (!mask) return fail(NPA_ERR_INVALID_ARGUMENT, "blur_gradient_backward: both upstream gradients are NULL");
-    FeatureBwdArgs a = {x_bin, mass, rho, s_bin, dL_dblur, dL_dgrad, grad_x, grad_s, grad_rho, channels, bin_offsets, block_info};
+    if ((rc = check_pair_cache("blur_gradient_backward", pair_cache, pair_stride)) != NPA_OK) return rc;
+    FeatureBwdArgs a = {x_bin, mass, rho, s_bin, dL_dblur, dL_dgrad, grad_x, grad_s, grad_rho, channels, bin_offsets, block_info,
+                        pair_cache, pair_stride};
     return launch_feature_backward(g, mask, grad_x || grad_rho, a, (cudaStream_t)stream);
 }
 
@@ -291,7 +302,7 @@ int npa_density_chain_backward(const npa_grid *gd, const float *x_bin, const flo
 int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *mass,
                            const float *s_bin, float *rho, float *count, float *rho_grad, float *s_blur,
                            float *s_grad, float *moment, const int32_t *bin_offsets,
-                           const int32_t *block_info, void *stream) {
+                           const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = begin_op("perception_forward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -306,8 +317,11 @@ int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_
         NPA_REQUIRE(s_bin, "perception_forward", "state_in");
         // the moment matrix shares every pair scalar with the gradient: fold it into the same sweep
         const bool fold = moment && fmask == (F_BLUR | F_GRAD);
+        if ((rc = check_pair_cache("perception_forward", pair_cache, pair_stride)) != NPA_OK) return rc;
         FeatureFwdArgs fa = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info,
                              fold ? moment : nullptr};
+        fa.pair_cache = pair_cache;
+        fa.pair_stride = pair_stride;
         if ((rc = launch_feature_forward(g, fold ? (fmask | F_MOMENT) : fmask, fa, st)) != NPA_OK) return rc;
         if (fold) moment = nullptr;
     }
@@ -324,7 +338,7 @@ int npa_perception_backward(const npa_grid *gd, int32_t channels, const float *x
                             const float *s_bin, const float *rho, const float *dL_drho_out,
                             const float *dL_dblur, const float *dL_dgrad, const float *dL_drho_grad,
                             float *grad_x, float *grad_s, float *grad_rho_scratch,
-                            const int32_t *bin_offsets, const int32_t *block_info, void *stream) {
+                            const int32_t *bin_offsets, const int32_t *block_info, const int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = begin_op("perception_backward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -339,8 +353,9 @@ int npa_perception_backward(const npa_grid *gd, int32_t channels, const float *x
         if ((rc = check_channels("perception_backward", channels)) != NPA_OK) return rc;
         NPA_REQUIRE(s_bin, "perception_backward", "state_in");
         NPA_REQUIRE(rho, "perception_backward", "rho");
+        if ((rc = check_pair_cache("perception_backward", pair_cache, pair_stride)) != NPA_OK) return rc;
         FeatureBwdArgs fa = {x_bin, mass, rho, s_bin, dL_dblur, dL_dgrad, grad_x, grad_s,
-                             full ? grad_rho_scratch : nullptr, channels, bin_offsets, block_info};
+                             full ? grad_rho_scratch : nullptr, channels, bin_offsets, block_info, pair_cache, pair_stride};
         if ((rc = launch_feature_backward(g, fmask, full, fa, st)) != NPA_OK) return rc;
         x_written = full;
     } else if (grad_s) {

@@ -157,6 +157,41 @@ __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x,
     flush(n);
 }
 
+// Stage 1 from a cached neighbour list (written by the forward sweep of the same snapshot): the
+// lanes fetch the listed positions and rebuild the displacements; no candidate is tested.  On a
+// periodic grid the image of each pair is recovered from the raw difference (x_j - x_i is within half
+// a box of a multiple of the box length) and applied with the same error-free shifted origin as the
+// cell walk uses.
+template <int D, bool PER>
+__device__ inline void expand_pairs(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
+                                    const int32_t *__restrict__ list, int count, float4 *geo) {
+    const int lane = threadIdx.x & 31;
+    for (int e = lane; e < count; e += 32) {
+        const int j = __ldg(list + e);
+        const Pos<D> pj = load_pos<D>(x, j);
+        float rx, ry, rz;
+        if (PER) {
+            const float pv[3] = {pi.x, pi.y, pi.z}, jv[3] = {pj.x, pj.y, pj.z};
+            float r[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                const float k = -rintf((jv[d] - pv[d]) * g.invL[d]);   // image shift in box lengths
+                const float b = -k * g.L[d];
+                const float sum = __fadd_rn(pv[d], b);
+                const float bb = __fsub_rn(sum, pv[d]);
+                const float err = __fadd_rn(__fsub_rn(pv[d], __fsub_rn(sum, bb)), __fsub_rn(b, bb));
+                r[d] = (jv[d] - sum) + __fsub_rn(k * g.Llo[d], err);
+            }
+            rx = r[0]; ry = r[1]; rz = r[2];
+        } else {
+            rx = pj.x - pi.x;
+            ry = pj.y - pi.y;
+            rz = D == 3 ? pj.z - pi.z : 0.f;
+        }
+        geo[e] = make_float4(rx, ry, rz, __int_as_float(j));
+    }
+}
+
 template <int D, bool PER, int LPP, int VW, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 feature_forward_kernel(FeatureFwdArgs a, Geom g) {
@@ -201,11 +236,14 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             for (int q = 0; q < VW * D; ++q) gr[q] = 0.f;
             if (fvalid && (MASK & F_GRAD)) load_feat<VW>(a.s + i * C + f0, si);
 
+            int cached = 0;  // pairs of this particle already written to the neighbour list cache
             auto flush = [&](int n) {
                 __syncwarp();
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
                     const float4 ge = geo[e];
                     const int j = __float_as_int(ge.w);
+                    if (a.pair_cache && fbase == 0 && cached + e < a.pair_stride - 1)
+                        a.pair_cache[i * a.pair_stride + 1 + cached + e] = j;
                     const float q = sq_norm_fast<D>(ge.x, ge.y, ge.z);
                     const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                     const float vj = mj / __ldg(a.rho + j);
@@ -269,9 +307,12 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     }
                     async_wait<0>();
                 }
+                cached += n;
                 __syncwarp();
             };
             collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
+            if (a.pair_cache && fbase == 0 && lane == 0)
+                a.pair_cache[i * a.pair_stride] = cached <= a.pair_stride - 1 ? cached : -1;
 
             if (MASK & F_BLUR) {
 #pragma unroll
@@ -580,7 +621,14 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                 }
                 __syncwarp();
             };
-            collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
+            int listed = -1;
+            if (a.pair_cache) listed = __ldg(a.pair_cache + i * a.pair_stride);
+            if (listed >= 0 && listed <= kListPerWarp) {
+                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
+                flush(listed);
+            } else {
+                collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
+            }
 
             if (a.grad_s) {
                 float out[VW];

@@ -58,6 +58,10 @@ struct FeatureFwdArgs {
     const float *rho_grad;   // [B,N,D] density gradient of the same positions
     float coef, dg_scale, inv_tol;
     int log_norm_grad, log_norm_dg;
+    // ---- neighbour list cache (optional): row i = [count | j_0 .. j_{count-1}], count = -1 when the
+    // particle has more than pair_stride - 1 neighbours (the reader then searches the cells itself)
+    int32_t *pair_cache;     // [B*N, pair_stride] written by this sweep, or NULL
+    int pair_stride;
 };
 
 struct FeatureBwdArgs {
@@ -73,6 +77,8 @@ struct FeatureBwdArgs {
     int C;
     const int32_t *bin_offsets;
     const int32_t *block_info;
+    const int32_t *pair_cache;  // neighbour lists written by the forward sweep of the same snapshot, or NULL
+    int pair_stride;
 };
 
 int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st);

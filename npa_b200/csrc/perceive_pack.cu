@@ -87,7 +87,7 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
                                   const float *s_bin, float coef, float dg_scale, float inv_tol,
                                   int32_t log_norm_grad, int32_t log_norm_dg, float *rho, float *rho_grad,
                                   float *z, float *vgrad, const int32_t *bin_offsets, const int32_t *block_info,
-                                  void *stream) {
+                                  int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = make_geom(gd, &g);
     if (rc != NPA_OK) return rc;
@@ -109,6 +109,10 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
     fa.inv_tol = inv_tol;
     fa.log_norm_grad = log_norm_grad;
     fa.log_norm_dg = log_norm_dg;
+    if (pair_cache && (pair_stride < 2 || pair_stride > 129))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 129]");
+    fa.pair_cache = pair_cache;
+    fa.pair_stride = pair_stride;
     return launch_feature_forward(g, F_BLUR | F_GRAD | F_MOMENT | F_PACK, fa, st);
 }
 
@@ -118,7 +122,8 @@ int npa_perceive_features_backward(const npa_grid *gd, int32_t channels, const f
                                    int32_t log_norm_grad, int32_t log_norm_dg, float *g_blur_scratch,
                                    float *g_grad_scratch, float *g_rho_grad_scratch, float *grad_rho_scratch,
                                    float *grad_x, float *grad_s, const int32_t *bin_offsets,
-                                   const int32_t *block_info, void *stream) {
+                                   const int32_t *block_info, const int32_t *pair_cache, int32_t pair_stride,
+                                   void *stream) {
     Geom g;
     int rc = make_geom(gd, &g);
     if (rc != NPA_OK) return rc;
@@ -140,7 +145,7 @@ int npa_perceive_features_backward(const npa_grid *gd, int32_t channels, const f
                                                         particles, channels, coef, dg_scale, log_norm_grad, log_norm_dg);
     if ((rc = check_launch("pack_backward_kernel")) != NPA_OK) return rc;
     rc = npa_perception_backward(gd, channels, x_bin, mass, s_bin, rho, nullptr, g_blur_scratch, g_grad_scratch, grg,
-                                 grad_x, grad_s, grad_rho_scratch, bin_offsets, block_info, stream);
+                                 grad_x, grad_s, grad_rho_scratch, bin_offsets, block_info, pair_cache, pair_stride, stream);
     if (rc != NPA_OK) return rc;
     if (grad_s) {
         add_direct_kernel<<<blocks, 256, 0, st>>>(dL_dz, grad_s, particles, channels,

@@ -124,6 +124,26 @@ class HashGrid:
 # is fused too.  Off by default: a caller that only wants blur would pay for the gradient.
 # ---------------------------------------------------------------------------------------------
 _FUSION = {"enabled": False}
+# Columns of the neighbour-list cache the fused forward passes write for their backward pass
+# (row = count, j_0, j_1, ...; particles with more neighbours are searched again); 0 = off.
+_PAIR_CACHE = {"columns": 64}
+
+
+def set_pair_cache(columns=64):
+    """Size of the per-particle neighbour list the fused forward sweeps keep for their backward
+    (4 * columns bytes per particle while the autograd graph is alive); 0 disables it."""
+    columns = int(columns)
+    if columns != 0 and not 2 <= columns <= 129:
+        raise ValueError("columns must be 0 or between 2 and 129")
+    _PAIR_CACHE["columns"] = columns
+
+
+def _new_pair_cache(s_bin, wanted):
+    K = _PAIR_CACHE["columns"]
+    if not wanted or K == 0:
+        return None
+    B, N = s_bin.shape[:2]
+    return torch.empty(B, N, K, dtype=torch.int32, device=s_bin.device)
 
 
 def enable_fusion(flag=True):
@@ -197,9 +217,11 @@ class BlurGradient(torch.autograd.Function):
         s_blur = torch.empty_like(s_bin)
         s_grad = torch.empty(B, N, C, dim, dtype=torch.float32, device=dev)
         moment = torch.empty(B, N, dim, dim, dtype=torch.float32, device=dev)
+        pairs = _new_pair_cache(s_bin, x_bin.requires_grad or s_bin.requires_grad or rho.requires_grad)
         snapshot.grid.blur_gradient_forward(x_bin, rho, mass, s_bin, s_blur, s_grad, snapshot.bin_offsets,
-                                            snapshot.block_info, moment)
+                                            snapshot.block_info, moment, pair_cache=pairs)
         ctx.save_for_backward(x_bin, s_bin, rho, *([] if mass is None else [mass]))
+        ctx.pairs = pairs
         ctx.has_mass = mass is not None
         ctx.snapshot = snapshot
         ctx.needs = (x_bin.requires_grad, s_bin.requires_grad, rho.requires_grad)
@@ -220,7 +242,7 @@ class BlurGradient(torch.autograd.Function):
         grad_s = torch.empty_like(s_bin) if dLds else None
         grad_rho = torch.empty_like(rho) if dLdrho else None
         snap.grid.blur_gradient_backward(x_bin, rho, mass, s_bin, cont(g_blur), cont(g_grad), grad_x, grad_s,
-                                         grad_rho, snap.bin_offsets, snap.block_info)
+                                         grad_rho, snap.bin_offsets, snap.block_info, pair_cache=ctx.pairs)
         return grad_x, grad_s, grad_rho, None, None
 
 
@@ -469,8 +491,10 @@ class Perception(torch.autograd.Function):
         s_blur = torch.empty_like(s_bin)
         s_grad = torch.empty(B, N, C, dim, dtype=torch.float32, device=dev)
         rho_grad = torch.empty(B, N, dim, dtype=torch.float32, device=dev) if want_density_gradient else None
+        pairs = _new_pair_cache(s_bin, x_bin.requires_grad or s_bin.requires_grad)
         snapshot.grid.perception_forward(x_bin, mass, s_bin, rho, None, rho_grad, s_blur, s_grad, None,
-                                         snapshot.bin_offsets, snapshot.block_info)
+                                         snapshot.bin_offsets, snapshot.block_info, pair_cache=pairs)
+        ctx.pairs = pairs
         ctx.save_for_backward(x_bin, s_bin, rho, *([] if mass is None else [mass]))
         ctx.has_mass = mass is not None
         ctx.snapshot = snapshot
@@ -494,7 +518,7 @@ class Perception(torch.autograd.Function):
         if dLdx or dLds:
             snap.grid.perception_backward(x_bin, mass, s_bin, rho, cont(g_rho) if dLdx else None, cont(g_blur),
                                           cont(g_grad), cont(g_rho_grad) if dLdx else None, grad_x, grad_s,
-                                          scratch, snap.bin_offsets, snap.block_info)
+                                          scratch, snap.bin_offsets, snap.block_info, pair_cache=ctx.pairs)
         return grad_x, grad_s, None, None, None
 
 
@@ -523,9 +547,11 @@ class PerceiveFeatures(torch.autograd.Function):
         z = torch.empty(B, N, 2 * C + C * D + D, **f32)
         keep = x_bin.requires_grad or s_bin.requires_grad
         vgrad = torch.empty(B, N, C, D, **f32) if keep else None
+        pairs = _new_pair_cache(s_bin, keep)
         snapshot.grid.perceive_features_forward(x_bin, mass, s_bin, coef, dg_scale, inv_tol, log_norm_grad,
                                                 log_norm_dg, rho, rho_grad, z, vgrad, snapshot.bin_offsets,
-                                                snapshot.block_info)
+                                                snapshot.block_info, pair_cache=pairs)
+        ctx.pairs = pairs
         if keep:
             ctx.save_for_backward(x_bin, s_bin, rho, rho_grad, vgrad, *([] if mass is None else [mass]))
         ctx.has_mass = mass is not None
@@ -552,7 +578,7 @@ class PerceiveFeatures(torch.autograd.Function):
         grad_rho = torch.empty_like(rho) if dLdx else None
         snap.grid.perceive_features_backward(x_bin, mass, s_bin, rho, rho_grad, vgrad, g_z.contiguous(), coef,
                                              dg_scale, ln_g, ln_dg, g_blur, g_grad, g_rho_grad, grad_rho, grad_x,
-                                             grad_s, snap.bin_offsets, snap.block_info)
+                                             grad_s, snap.bin_offsets, snap.block_info, pair_cache=ctx.pairs)
         return (grad_x, grad_s if dLds else None) + (None,) * 7
 
 

@@ -111,6 +111,16 @@ class _HashGridBase:
             self._scratch = torch.empty(self._scratch_bytes, dtype=torch.uint8, device=device)
         return self._scratch
 
+    def _pairs(self, pair_cache):
+        """(pointer, stride) of an optional neighbour-list cache ``[B, N, K]`` int32, 2 <= K <= 129."""
+        if pair_cache is None:
+            return None, 0
+        K = pair_cache.shape[-1] if isinstance(pair_cache, torch.Tensor) and pair_cache.dim() == 3 else -1
+        _check(pair_cache, (self._B, self._N, K), "pair_cache", torch.int32)
+        if not 2 <= K <= 129:
+            raise RuntimeError(f"pair_cache must have between 2 and 129 columns, got {K}")
+        return N.ptr(pair_cache), K
+
     @staticmethod
     def _call(fn, tensor_for_device, *args):
         with torch.cuda.device(tensor_for_device.device):
@@ -300,7 +310,7 @@ class _HashGridBase:
 
     # ---- fused sweeps (no counterpart in the reference module) ------------------
     def blur_gradient_forward(self, binned_positions, rho, mass, state_in, state_out, state_gradient_out,
-                              bin_offsets, block_info, moment_matrix_out=None):
+                              bin_offsets, block_info, moment_matrix_out=None, pair_cache=None):
         """blur and gradient in one launch; ``mass`` and either output may be None.  With
         ``moment_matrix_out`` (and both other outputs) the moment matrix rides the same sweep."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
@@ -320,10 +330,10 @@ class _HashGridBase:
             return
         self._call(_lib.npa_blur_gradient_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(state_out), N.ptr(state_gradient_out),
-                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
     def blur_gradient_backward(self, binned_positions, rho, mass, state_in, dL_blur_state_out, dL_grad_state_out,
-                               grad_x, grad_s, grad_rho, bin_offsets, block_info):
+                               grad_x, grad_s, grad_rho, bin_offsets, block_info, pair_cache=None):
         """Backward of both feature operators in one launch; None outputs are not computed."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
         self._pos(binned_positions, "binned_positions")
@@ -346,7 +356,8 @@ class _HashGridBase:
             return
         self._call(_lib.npa_blur_gradient_backward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(dL_blur_state_out), N.ptr(dL_grad_state_out),
-                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(grad_rho), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(grad_rho), N.ptr(bin_offsets), N.ptr(block_info),
+                   *self._pairs(pair_cache))
 
     def density_chain_backward(self, binned_positions, mass, dL_rho_a, dL_rho_b, dL_density_gradient_out, grad_x,
                                accumulate, bin_offsets, block_info):
@@ -369,7 +380,7 @@ class _HashGridBase:
     # ---- packed perception (no counterpart in the reference module) ------------
     def perceive_features_forward(self, binned_positions, mass, state_in, coef, dg_scale, inv_tol, log_norm_grad,
                                   log_norm_dg, rho, density_gradient_out, z, corrected_gradient_out, bin_offsets,
-                                  block_info):
+                                  block_info, pair_cache=None):
         """Two sweeps that write the packed perception row z; ``mass`` and ``corrected_gradient_out`` may be None."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
         D = self._dim
@@ -386,11 +397,12 @@ class _HashGridBase:
         self._call(_lib.npa_perceive_features_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(mass), N.ptr(state_in), float(coef), float(dg_scale), float(inv_tol),
                    1 if log_norm_grad else 0, 1 if log_norm_dg else 0, N.ptr(rho), N.ptr(density_gradient_out),
-                   N.ptr(z), N.ptr(corrected_gradient_out), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(z), N.ptr(corrected_gradient_out), N.ptr(bin_offsets), N.ptr(block_info),
+                   *self._pairs(pair_cache))
 
     def perceive_features_backward(self, binned_positions, mass, state_in, rho, density_gradient, corrected_gradient,
                                    dL_dz, coef, dg_scale, log_norm_grad, log_norm_dg, g_blur_scratch, g_grad_scratch,
-                                   g_rho_grad_scratch, grad_rho_scratch, grad_x, grad_s, bin_offsets, block_info):
+                                   g_rho_grad_scratch, grad_rho_scratch, grad_x, grad_s, bin_offsets, block_info, pair_cache=None):
         """Backward of ``perceive_features_forward``; ``grad_x`` (and its two scratch tensors) may be None."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
         D = self._dim
@@ -415,11 +427,11 @@ class _HashGridBase:
                    N.ptr(mass), N.ptr(state_in), N.ptr(rho), N.ptr(density_gradient), N.ptr(corrected_gradient),
                    N.ptr(dL_dz), float(coef), float(dg_scale), 1 if log_norm_grad else 0, 1 if log_norm_dg else 0,
                    N.ptr(g_blur_scratch), N.ptr(g_grad_scratch), N.ptr(g_rho_grad_scratch), N.ptr(grad_rho_scratch),
-                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(grad_x), N.ptr(grad_s), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
     # ---- fused perception (no counterpart in the reference module) -------------
     def perception_forward(self, binned_positions, mass, state_in, rho, count, density_gradient_out,
-                           state_out, state_gradient_out, moment_matrix_out, bin_offsets, block_info):
+                           state_out, state_gradient_out, moment_matrix_out, bin_offsets, block_info, pair_cache=None):
         """rho is required; every other output and ``mass`` may be None."""
         self._pos(binned_positions, "binned_positions")
         self._bn(rho, "rho")
@@ -443,11 +455,11 @@ class _HashGridBase:
         self._call(_lib.npa_perception_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(mass), N.ptr(state_in if C else None), N.ptr(rho), N.ptr(count),
                    N.ptr(density_gradient_out), N.ptr(state_out), N.ptr(state_gradient_out),
-                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
     def perception_backward(self, binned_positions, mass, state_in, rho, dL_rho_out, dL_blur_state_out,
                             dL_grad_state_out, dL_density_gradient_out, grad_x, grad_s, grad_rho_scratch,
-                            bin_offsets, block_info):
+                            bin_offsets, block_info, pair_cache=None):
         """Chained backward; upstreams, ``mass``, ``grad_x`` and ``grad_s`` may be None."""
         self._pos(binned_positions, "binned_positions")
         self._bn(rho, "rho")
@@ -473,7 +485,7 @@ class _HashGridBase:
         self._call(_lib.npa_perception_backward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(mass), N.ptr(state_in), N.ptr(rho), N.ptr(dL_rho_out), N.ptr(dL_blur_state_out),
                    N.ptr(dL_grad_state_out), N.ptr(dL_density_gradient_out), N.ptr(grad_x), N.ptr(grad_s),
-                   N.ptr(grad_rho_scratch), N.ptr(bin_offsets), N.ptr(block_info))
+                   N.ptr(grad_rho_scratch), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
 
 def _make(name, dim, boundary, mode):
