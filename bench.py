@@ -241,7 +241,7 @@ def run_gpu_arm(args, w):
     blur = torch.empty(B, N, C, **f32)
     grad = torch.empty(B, N, C, D, **f32)
     grad_x, grad_s, grad_rho = torch.empty_like(x_d), torch.empty_like(s_d), torch.empty(B, N, **f32)
-    pairs = torch.empty(B, N, 64, **i32)  # neighbour lists: written by the forward sweep, read by the backward
+    pairs = torch.empty(B, N, 64, **i32)  # neighbour lists: written by the density sweep, read by the other three
     mlp_grad = torch.zeros(MLP_GRAD_FLOATS, **f32)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB of L2
     phases = ["grid_build", "reorder", "density_sweep", "blur_gradient_sweep", "blur_gradient_backward",
@@ -255,14 +255,15 @@ def run_gpu_arm(args, w):
         mark(1)
         hg.bin_particles(x_d, s_d, None, perm, x_bin, s_bin, None)
         mark(2)
-        hg.perception_forward(x_bin, None, None, rho, None, None, None, None, None, offs, info)
+        hg.perception_forward(x_bin, None, None, rho, None, None, None, None, None, offs, info, pair_cache=pairs)
         mark(3)
-        hg.blur_gradient_forward(x_bin, rho, None, s_bin, blur, grad, offs, info, pair_cache=pairs)
+        hg.blur_gradient_forward(x_bin, rho, None, s_bin, blur, grad, offs, info, pair_cache=pairs,
+                                 pair_cache_valid=True)
         mark(4)
         hg.blur_gradient_backward(x_bin, rho, None, s_bin, ups["g_blur"], ups["g_grad"], grad_x, grad_s,
                                   grad_rho, offs, info, pair_cache=pairs)
         mark(5)
-        hg.density_chain_backward(x_bin, None, ups["g_rho"], grad_rho, None, grad_x, True, offs, info)
+        hg.density_chain_backward(x_bin, None, ups["g_rho"], grad_rho, None, grad_x, True, offs, info, pair_cache=pairs)
         if world > 1:
             dist.all_reduce(mlp_grad)  # the only exchange of data-parallel training: the MLP gradients
         mark(6)

@@ -233,14 +233,18 @@ int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
                          float tol, void *stream);
 
 /* ---- neighbour list cache ---------------------------------------------------- *
- * Forward and backward of one snapshot visit the same pairs.  The fused entry
- * points below take an optional cache  pair_cache [B*N, pair_stride] (int32,
- * caller-allocated; NULL = off): the forward blur/gradient sweep records, per
- * particle, the number of accepted neighbours and their indices (row = count,
- * j_0, j_1, ...; count = -1 when there are more than pair_stride - 1), and the
- * backward sweep given the same cache rebuilds the displacements from the list
- * instead of testing the ~3^D cells of candidates again (particles marked -1 are
- * searched as usual).  pair_stride <= 129.  No counterpart in the reference.   */
+ * All sweeps over one snapshot visit the same pairs.  The fused entry points
+ * below take an optional cache  pair_cache [B*N, pair_stride] (int32,
+ * caller-allocated; NULL = off): the first sweep that searches the cells (the
+ * density sweep of npa_perception_forward / npa_perceive_features_forward, or
+ * npa_blur_gradient_forward with pair_cache_valid == 0) records, per particle,
+ * the number of accepted neighbours and their indices (row = count, j_0, j_1,
+ * ...; count = -1 when there are more than pair_stride - 1); every later sweep
+ * given the same cache (pair_cache_valid != 0 for a forward sweep; all backward
+ * sweeps) rebuilds the displacements from the list instead of testing the ~3^D
+ * cells of candidates again (particles marked -1 are searched as usual).
+ * The cache belongs to one snapshot AND one set of positions.  2 <= pair_stride
+ * <= 129.  No counterpart in the reference.                                   */
 
 /* ---- blur + gradient in one launch ------------------------------------------ *
  * The two feature operators share every pair test and every neighbour feature
@@ -253,7 +257,8 @@ int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
 int npa_blur_gradient_forward(const npa_grid *g, int32_t channels, const float *x_bin,
                               const float *rho, const float *mass, const float *s_bin,
                               float *s_blur, float *s_grad, float *moment,
-                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream);
+                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride,
+                              int32_t pair_cache_valid, void *stream);
 
 /* grad_x == NULL and grad_rho == NULL selects the variant that differentiates
  * with respect to s only. */
@@ -275,7 +280,8 @@ int npa_density_chain_backward(const npa_grid *g, const float *x_bin, const floa
                                const float *dL_drho_a, const float *dL_drho_b,
                                const float *dL_drho_grad, float *grad_x, int32_t accumulate,
                                const int32_t *bin_offsets, const int32_t *block_info,
-                               void *stream);
+                               const int32_t *pair_cache,
+                               int32_t pair_stride, void *stream);
 
 /* ---- fused perception (one launch set for what NPA.perceive asks for) ---- *
  * The reference runs density, blur, gradient, density_gradient and

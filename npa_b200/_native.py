@@ -66,9 +66,9 @@ SIGNATURES = {
     "npa_density_gradient_backward": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
     "npa_moment_matrix_backward": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "npa_safe_inv_sym_mat": (ctypes.c_int, [_I32, _I64, _P, _P, ctypes.c_float, _P]),
-    "npa_blur_gradient_forward": (ctypes.c_int, [_P, _I32] + [_P] * 9 + [_P, _I32, _P]),
+    "npa_blur_gradient_forward": (ctypes.c_int, [_P, _I32] + [_P] * 9 + [_P, _I32, _I32, _P]),
     "npa_blur_gradient_backward": (ctypes.c_int, [_P, _I32] + [_P] * 11 + [_P, _I32, _P]),
-    "npa_density_chain_backward": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _I32, _P, _P, _P]),
+    "npa_density_chain_backward": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _I32, _P, _P, _P, _I32, _P]),
     "npa_perceive_features_forward": (ctypes.c_int, [_P, _I32, _P, _P, _P, ctypes.c_float, ctypes.c_float,
                                                      ctypes.c_float, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _P]),
     "npa_perceive_features_backward": (ctypes.c_int, [_P, _I32] + [_P] * 7 + [ctypes.c_float, ctypes.c_float, _I32, _I32]

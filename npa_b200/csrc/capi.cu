@@ -242,7 +242,7 @@ int npa_gradient_backward(const npa_grid *gd, int32_t channels, const float *x_b
 
 int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float *x_bin, const float *rho,
                               const float *mass, const float *s_bin, float *s_blur, float *s_grad, float *moment,
-                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, void *stream) {
+                              const int32_t *bin_offsets, const int32_t *block_info, int32_t *pair_cache, int32_t pair_stride, int32_t pair_cache_valid, void *stream) {
     Geom g;
     int rc = begin_op("blur_gradient_forward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -260,6 +260,7 @@ int npa_blur_gradient_forward(const npa_grid *gd, int32_t channels, const float 
     FeatureFwdArgs a = {x_bin, mass, rho, s_bin, s_blur, s_grad, channels, bin_offsets, block_info, moment};
     a.pair_cache = pair_cache;
     a.pair_stride = pair_stride;
+    a.pair_cache_valid = pair_cache && pair_cache_valid;
     return launch_feature_forward(g, mask, a, (cudaStream_t)stream);
 }
 
@@ -286,7 +287,7 @@ int npa_blur_gradient_backward(const npa_grid *gd, int32_t channels, const float
 int npa_density_chain_backward(const npa_grid *gd, const float *x_bin, const float *mass, const float *dL_drho_a,
                                const float *dL_drho_b, const float *dL_drho_grad, float *grad_x,
                                int32_t accumulate, const int32_t *bin_offsets, const int32_t *block_info,
-                               void *stream) {
+                               const int32_t *pair_cache, int32_t pair_stride, void *stream) {
     Geom g;
     int rc = begin_op("density_chain_backward", gd, &g, x_bin, bin_offsets, block_info);
     if (rc != NPA_OK) return rc;
@@ -294,8 +295,9 @@ int npa_density_chain_backward(const npa_grid *gd, const float *x_bin, const flo
     if ((rc = check_grad_x("density_chain_backward", g, grad_x)) != NPA_OK) return rc;
     const int mask = ((dL_drho_a || dL_drho_b) ? S_DENSITY : 0) | (dL_drho_grad ? S_DGRAD : 0);
     if (!mask) return fail(NPA_ERR_INVALID_ARGUMENT, "density_chain_backward: every upstream gradient is NULL");
+    if ((rc = check_pair_cache("density_chain_backward", pair_cache, pair_stride)) != NPA_OK) return rc;
     ScalarBwdArgs a = {x_bin, mass, nullptr, dL_drho_a, dL_drho_b, dL_drho_grad, nullptr, grad_x, nullptr,
-                       accumulate ? 1 : 0, bin_offsets, block_info};
+                       accumulate ? 1 : 0, bin_offsets, block_info, pair_cache, pair_stride};
     return launch_scalar_backward(g, mask, a, (cudaStream_t)stream);
 }
 
@@ -309,7 +311,8 @@ int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_
     NPA_REQUIRE(rho, "perception_forward", "rho");
     cudaStream_t st = (cudaStream_t)stream;
     int smask = S_DENSITY | (count ? S_COUNT : 0) | (rho_grad ? S_DGRAD : 0);
-    ScalarFwdArgs sa = {x_bin, mass, nullptr, count, rho, rho_grad, nullptr, bin_offsets, block_info};
+    if ((rc = check_pair_cache("perception_forward", pair_cache, pair_stride)) != NPA_OK) return rc;
+    ScalarFwdArgs sa = {x_bin, mass, nullptr, count, rho, rho_grad, nullptr, bin_offsets, block_info, pair_cache, pair_stride};
     if ((rc = launch_scalar_forward(g, smask, sa, st)) != NPA_OK) return rc;
     const int fmask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
     if (fmask) {
@@ -322,6 +325,7 @@ int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_
                              fold ? moment : nullptr};
         fa.pair_cache = pair_cache;
         fa.pair_stride = pair_stride;
+        fa.pair_cache_valid = pair_cache != nullptr;  // written by the density sweep above
         if ((rc = launch_feature_forward(g, fold ? (fmask | F_MOMENT) : fmask, fa, st)) != NPA_OK) return rc;
         if (fold) moment = nullptr;
     }
@@ -368,7 +372,7 @@ int npa_perception_backward(const npa_grid *gd, int32_t channels, const float *x
         const int smask = ((ga || gb) ? S_DENSITY : 0) | (dL_drho_grad ? S_DGRAD : 0);
         if (smask) {
             ScalarBwdArgs sa = {x_bin, mass, nullptr, ga, gb, dL_drho_grad, nullptr, grad_x, nullptr,
-                                x_written ? 1 : 0, bin_offsets, block_info};
+                                x_written ? 1 : 0, bin_offsets, block_info, pair_cache, pair_stride};
             if ((rc = launch_scalar_backward(g, smask, sa, st)) != NPA_OK) return rc;
         } else if (!x_written) {
             cudaError_t e = cudaMemsetAsync(grad_x, 0, sizeof(float) * (size_t)g.B * g.N * (g.dim == 2 ? 2 : 4), st);

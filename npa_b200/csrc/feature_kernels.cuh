@@ -90,15 +90,6 @@ __device__ inline void async_wait() { asm volatile("cp.async.wait_group %0;\n" :
 template <int VW> struct Piece { float v[VW]; };
 template <> struct __align__(16) Piece<4> { float v[4]; };
 
-// Number of CTAs of a persistent launch of `kernel`: every SM filled to the kernel's occupancy.
-// Cached per (device, kernel); the first call also raises the kernel's dynamic shared-memory
-// limit to what its staging ring needs.  Defined in capi.cu.
-int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *out);
-template <typename Kernel>
-int persistent_ctas(Kernel kernel, int threads, size_t dyn_smem, int *out) {
-    return persistent_ctas_impl(reinterpret_cast<const void *>(kernel), threads, dyn_smem, out);
-}
-
 // Sum over the sub-groups of a warp: lanes with equal (lane % LPP) are combined.
 template <int LPP>
 __device__ inline float across_subgroups(float v) {
@@ -109,51 +100,21 @@ __device__ inline float across_subgroups(float v) {
 
 // Stage 1 for one particle: test every candidate of every range, append the
 // accepted displacements (r, index of j) to `geo`; calls flush(n) whenever the
-// list could overflow and once at the end.  The position of the next round's
-// candidate is loaded before the current round is tested, so the load latency
-// overlaps the test.
+// list could overflow and once at the end.
 template <int D, bool PER, typename Flush>
 __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
                                      const int4 *rng, int nr, float4 *geo, Flush &&flush) {
     const int lane = threadIdx.x & 31;
     int n = 0;
-    if (nr > 0) {
-        int r = 0;
-        int4 rg = rng[0];
-        int j0 = rg.x;
-        Pos<D> pj = {0.f, 0.f, 0.f};
-        if (j0 + lane < rg.y) pj = load_pos<D>(x, j0 + lane);
-        Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-        while (true) {
-            // locate and prefetch the next round
-            int nxt_r = r, nxt_j0 = j0 + 32;
-            int4 nxt_rg = rg;
-            if (nxt_j0 >= rg.y) {
-                nxt_r = r + 1;
-                if (nxt_r < nr) {
-                    nxt_rg = rng[nxt_r];
-                    nxt_j0 = nxt_rg.x;
-                }
-            }
-            Pos<D> pn = {0.f, 0.f, 0.f};
-            if (nxt_r < nr && nxt_j0 + lane < nxt_rg.y) pn = load_pos<D>(x, nxt_j0 + lane);
-            // test the current round
-            const int j = j0 + lane;
-            float rx = 0.f, ry = 0.f, rz = 0.f;
-            bool acc = false;
-            if (j < rg.y) acc = displacement<D, PER, false>(g, org, pj.x, pj.y, pj.z, rx, ry, rz) < g.h2;
-            const unsigned bal = __ballot_sync(kFull, acc);
-            if (acc) geo[n + __popc(bal & ((1u << lane) - 1u))] = make_float4(rx, ry, rz, __int_as_float(j));
-            n += __popc(bal);
-            if (n + 32 > kListPerWarp) {
-                flush(n);
-                n = 0;
-            }
-            if (nxt_r >= nr) break;
-            if (PER && nxt_r != r) org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, nxt_rg.z);
-            r = nxt_r; rg = nxt_rg; j0 = nxt_j0; pj = pn;
+    scan_candidates<D, PER, false>(g, x, pi, rng, nr, [&](bool acc, int j, float rx, float ry, float rz, float) {
+        const unsigned bal = __ballot_sync(kFull, acc);
+        if (acc) geo[n + __popc(bal & ((1u << lane) - 1u))] = make_float4(rx, ry, rz, __int_as_float(j));
+        n += __popc(bal);
+        if (n + 32 > kListPerWarp) {
+            flush(n);
+            n = 0;
         }
-    }
+    });
     flush(n);
 }
 
@@ -170,24 +131,7 @@ __device__ inline void expand_pairs(const Geom &g, const float *__restrict__ x, 
         const int j = __ldg(list + e);
         const Pos<D> pj = load_pos<D>(x, j);
         float rx, ry, rz;
-        if (PER) {
-            const float pv[3] = {pi.x, pi.y, pi.z}, jv[3] = {pj.x, pj.y, pj.z};
-            float r[3] = {0.f, 0.f, 0.f};
-#pragma unroll
-            for (int d = 0; d < D; ++d) {
-                const float k = -rintf((jv[d] - pv[d]) * g.invL[d]);   // image shift in box lengths
-                const float b = -k * g.L[d];
-                const float sum = __fadd_rn(pv[d], b);
-                const float bb = __fsub_rn(sum, pv[d]);
-                const float err = __fadd_rn(__fsub_rn(pv[d], __fsub_rn(sum, bb)), __fsub_rn(b, bb));
-                r[d] = (jv[d] - sum) + __fsub_rn(k * g.Llo[d], err);
-            }
-            rx = r[0]; ry = r[1]; rz = r[2];
-        } else {
-            rx = pj.x - pi.x;
-            ry = pj.y - pi.y;
-            rz = D == 3 ? pj.z - pi.z : 0.f;
-        }
+        listed_displacement<D, PER>(g, pi, pj, rx, ry, rz);
         geo[e] = make_float4(rx, ry, rz, __int_as_float(j));
     }
 }
@@ -242,7 +186,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
                     const float4 ge = geo[e];
                     const int j = __float_as_int(ge.w);
-                    if (a.pair_cache && fbase == 0 && cached + e < a.pair_stride - 1)
+                    if (a.pair_cache && !a.pair_cache_valid && fbase == 0 && cached + e < a.pair_stride - 1)
                         a.pair_cache[i * a.pair_stride + 1 + cached + e] = j;
                     const float q = sq_norm_fast<D>(ge.x, ge.y, ge.z);
                     const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
@@ -310,9 +254,16 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 cached += n;
                 __syncwarp();
             };
-            collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
-            if (a.pair_cache && fbase == 0 && lane == 0)
-                a.pair_cache[i * a.pair_stride] = cached <= a.pair_stride - 1 ? cached : -1;
+            int listed = -1;
+            if (a.pair_cache && a.pair_cache_valid) listed = __ldg(a.pair_cache + i * a.pair_stride);
+            if (listed >= 0 && listed <= kListPerWarp) {
+                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
+                flush(listed);
+            } else {
+                collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
+                if (a.pair_cache && !a.pair_cache_valid && fbase == 0 && lane == 0)
+                    a.pair_cache[i * a.pair_stride] = cached <= a.pair_stride - 1 ? cached : -1;
+            }
 
             if (MASK & F_BLUR) {
 #pragma unroll

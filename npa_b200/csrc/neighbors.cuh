@@ -190,6 +190,74 @@ __device__ inline float displacement(const Geom &g, const Origin<D, PER> &o, flo
     return EXACT ? sq_norm<D>(rx, ry, rz) : sq_norm_fast<D>(rx, ry, rz);
 }
 
+// Visits every candidate of every range of one particle, 32 per round: body(acc, j, rx, ry, rz, q)
+// is called by all lanes once per round (acc = this lane's candidate exists and is within the
+// cut-off).  The position of the next round's candidate is loaded before the current round is
+// tested, so the load latency overlaps the test.  EXACT selects the contraction-free r^2.
+template <int D, bool PER, bool EXACT, typename Body>
+__device__ inline void scan_candidates(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
+                                       const int4 *rng, int nr, Body &&body) {
+    if (nr <= 0) return;
+    const int lane = threadIdx.x & 31;
+    int r = 0;
+    int4 rg = rng[0];
+    int j0 = rg.x;
+    Pos<D> pj = {0.f, 0.f, 0.f};
+    if (j0 + lane < rg.y) pj = load_pos<D>(x, j0 + lane);
+    Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
+    while (true) {
+        int nxt_r = r, nxt_j0 = j0 + 32;
+        int4 nxt_rg = rg;
+        if (nxt_j0 >= rg.y) {
+            nxt_r = r + 1;
+            if (nxt_r < nr) {
+                nxt_rg = rng[nxt_r];
+                nxt_j0 = nxt_rg.x;
+            }
+        }
+        Pos<D> pn = {0.f, 0.f, 0.f};
+        if (nxt_r < nr && nxt_j0 + lane < nxt_rg.y) pn = load_pos<D>(x, nxt_j0 + lane);
+        const int j = j0 + lane;
+        float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
+        bool acc = false;
+        if (j < rg.y) {
+            q = displacement<D, PER, EXACT>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
+            acc = q < g.h2;
+        }
+        body(acc, j, rx, ry, rz, q);
+        if (nxt_r >= nr) break;
+        if (PER && nxt_r != r) org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, nxt_rg.z);
+        r = nxt_r; rg = nxt_rg; j0 = nxt_j0; pj = pn;
+    }
+}
+
+// Displacement x_j - x_i of a pair taken from a neighbour list (no cell walk, so no known image
+// shift): on a periodic grid the image is recovered from the raw difference, which lies within
+// half a box of a multiple of the box length, and applied through the same error-free shifted
+// origin the cell walk uses.
+template <int D, bool PER>
+__device__ inline void listed_displacement(const Geom &g, const Pos<D> &pi, const Pos<D> &pj, float &rx, float &ry,
+                                           float &rz) {
+    if (PER) {
+        const float pv[3] = {pi.x, pi.y, pi.z}, jv[3] = {pj.x, pj.y, pj.z};
+        float r[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            const float k = -rintf((jv[d] - pv[d]) * g.invL[d]);  // image shift in box lengths
+            const float b = -k * g.L[d];
+            const float sum = __fadd_rn(pv[d], b);
+            const float bb = __fsub_rn(sum, pv[d]);
+            const float err = __fadd_rn(__fsub_rn(pv[d], __fsub_rn(sum, bb)), __fsub_rn(b, bb));
+            r[d] = (jv[d] - sum) + __fsub_rn(k * g.Llo[d], err);
+        }
+        rx = r[0]; ry = r[1]; rz = r[2];
+    } else {
+        rx = pj.x - pi.x;
+        ry = pj.y - pi.y;
+        rz = D == 3 ? pj.z - pi.z : 0.f;
+    }
+}
+
 // Sum over the LPP lanes of a sub-group (LPP a power of two <= 32).
 template <int LPP>
 __device__ inline float subgroup_sum(float v) {

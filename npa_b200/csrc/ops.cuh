@@ -23,6 +23,8 @@ struct ScalarFwdArgs {
     float *moment;        // [B,N,D,D]
     const int32_t *bin_offsets;
     const int32_t *block_info;
+    int32_t *pair_cache;  // neighbour lists to write ([B*N, pair_stride]) or NULL
+    int pair_stride;
 };
 
 struct ScalarBwdArgs {
@@ -38,6 +40,8 @@ struct ScalarBwdArgs {
     int accumulate_x;         // add into grad_x instead of overwriting
     const int32_t *bin_offsets;
     const int32_t *block_info;
+    const int32_t *pair_cache;  // neighbour lists of this snapshot to read, or NULL
+    int pair_stride;
 };
 
 struct FeatureFwdArgs {
@@ -60,8 +64,9 @@ struct FeatureFwdArgs {
     int log_norm_grad, log_norm_dg;
     // ---- neighbour list cache (optional): row i = [count | j_0 .. j_{count-1}], count = -1 when the
     // particle has more than pair_stride - 1 neighbours (the reader then searches the cells itself)
-    int32_t *pair_cache;     // [B*N, pair_stride] written by this sweep, or NULL
+    int32_t *pair_cache;     // [B*N, pair_stride] or NULL
     int pair_stride;
+    int pair_cache_valid;    // 0: this sweep writes the lists; 1: they are valid, read them instead of searching
 };
 
 struct FeatureBwdArgs {
@@ -80,6 +85,15 @@ struct FeatureBwdArgs {
     const int32_t *pair_cache;  // neighbour lists written by the forward sweep of the same snapshot, or NULL
     int pair_stride;
 };
+
+// Number of CTAs of a persistent launch of `kernel`: every SM filled to the kernel's occupancy.
+// Cached per (device, kernel); the first call also raises the kernel's dynamic shared-memory
+// limit to what it needs.  Defined in capi.cu.
+int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *out);
+template <typename Kernel>
+int persistent_ctas(Kernel kernel, int threads, size_t dyn_smem, int *out) {
+    return persistent_ctas_impl(reinterpret_cast<const void *>(kernel), threads, dyn_smem, out);
+}
 
 int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st);
 int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st);

@@ -97,7 +97,9 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
     if (((uintptr_t)x_bin % (g.dim == 2 ? 8 : 16)) || ((uintptr_t)block_info % 16))
         return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: positions / block_info are misaligned");
     cudaStream_t st = (cudaStream_t)stream;
-    ScalarFwdArgs sa = {x_bin, mass, nullptr, nullptr, rho, rho_grad, nullptr, bin_offsets, block_info};
+    if (pair_cache && (pair_stride < 2 || pair_stride > 129))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 129]");
+    ScalarFwdArgs sa = {x_bin, mass, nullptr, nullptr, rho, rho_grad, nullptr, bin_offsets, block_info, pair_cache, pair_stride};
     if ((rc = launch_scalar_forward(g, S_DENSITY | S_DGRAD, sa, st)) != NPA_OK) return rc;
     FeatureFwdArgs fa = {x_bin, mass, rho, s_bin, nullptr, nullptr, channels, bin_offsets, block_info, nullptr};
     fa.z = z;
@@ -113,6 +115,7 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
         return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 129]");
     fa.pair_cache = pair_cache;
     fa.pair_stride = pair_stride;
+    fa.pair_cache_valid = pair_cache != nullptr;  // written by the density sweep above
     return launch_feature_forward(g, F_BLUR | F_GRAD | F_MOMENT | F_PACK, fa, st);
 }
 

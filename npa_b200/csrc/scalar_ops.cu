@@ -7,107 +7,12 @@
 // (sphops/sph_cuda.cu:1418-1812 and 723-1416; pair math at :1160-1184,
 // :1236-1264, :1328-1375).  The backward is a gather: particle i accumulates
 // the terms of both roles it plays in a pair, so no global atomics are needed.
+// The forward sweep can also record each particle's accepted neighbours (the
+// neighbour-list cache) so that later sweeps of the same snapshot skip the search.
 #include "neighbors.cuh"
 #include "ops.cuh"
 
 namespace npa {
-
-constexpr int kScalarLpp = 4;                  // lanes per particle
-constexpr int kScalarPpw = 32 / kScalarLpp;    // particles per warp pass
-
-template <int D, bool PER, int MASK>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
-scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
-    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarpsPerCta + warp;
-    if (row >= g.max_blocks) return;
-    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
-    if (it.count <= 0) return;
-    int4 *rng = s_ranges[warp];
-    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
-    const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
-    constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
-    constexpr bool kPoly = (MASK & S_DENSITY) != 0;
-    constexpr int kSym = D * (D + 1) / 2;
-
-    for (int k0 = 0; k0 < it.count; k0 += kScalarPpw) {
-        const int k = k0 + sub;
-        const bool ivalid = k < it.count;
-        const long long i = it.first + (ivalid ? k : 0);
-        const Pos<D> pi = load_pos<D>(a.x, i);
-        float cnt = 0.f, rho = 0.f, dg[3] = {0.f, 0.f, 0.f}, mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < nr; ++r) {
-            const int4 rg = rng[r];
-            const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-            for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
-                const int j = j0 + sl;
-                if (!(ivalid && j < rg.y)) continue;
-                const Pos<D> pj = load_pos<D>(a.x, j);
-                float rx, ry, rz;
-                const float q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
-                if (!(q < g.h2)) continue;
-                if (MASK & S_COUNT) cnt += 1.0f;
-                const float mj = (kPoly || kSpiky) ? (a.mass ? __ldg(a.mass + j) : 1.0f) : 0.f;
-                if (kPoly) {
-                    const float t = fmaxf(g.h2 - q, 0.f);
-                    rho = fmaf(mj, t * t * t, rho);
-                }
-                if (kSpiky && q > 0.f) {
-                    float d;
-                    const float phi = spiky_phi(q, g.h, d);
-                    if (MASK & S_DGRAD) {
-                        const float w = mj * phi;
-                        dg[0] = fmaf(w, rx, dg[0]);
-                        dg[1] = fmaf(w, ry, dg[1]);
-                        if (D == 3) dg[2] = fmaf(w, rz, dg[2]);
-                    }
-                    if (MASK & S_MOMENT) {
-                        const float w = phi * mj / __ldg(a.rho_in + j);
-                        mom[0] = fmaf(w * rx, rx, mom[0]);
-                        mom[1] = fmaf(w * rx, ry, mom[1]);
-                        if (D == 2) {
-                            mom[2] = fmaf(w * ry, ry, mom[2]);
-                        } else {
-                            mom[2] = fmaf(w * rx, rz, mom[2]);
-                            mom[3] = fmaf(w * ry, ry, mom[3]);
-                            mom[4] = fmaf(w * ry, rz, mom[4]);
-                            mom[5] = fmaf(w * rz, rz, mom[5]);
-                        }
-                    }
-                }
-            }
-        }
-        // sub-group reduction (all 32 lanes take part) and write-out by lane 0 of each sub-group
-        if (MASK & S_COUNT) cnt = subgroup_sum<kScalarLpp>(cnt);
-        if (kPoly) rho = subgroup_sum<kScalarLpp>(rho);
-        if (MASK & S_DGRAD)
-#pragma unroll
-            for (int d = 0; d < D; ++d) dg[d] = subgroup_sum<kScalarLpp>(dg[d]);
-        if (MASK & S_MOMENT)
-#pragma unroll
-            for (int d = 0; d < kSym; ++d) mom[d] = subgroup_sum<kScalarLpp>(mom[d]);
-        if (ivalid && sl == 0) {
-            if ((MASK & S_COUNT) && a.count) a.count[i] = cnt;
-            if (kPoly && a.rho_out) a.rho_out[i] = g.c_s * rho;
-            if ((MASK & S_DGRAD) && a.rho_grad) {
-#pragma unroll
-                for (int d = 0; d < D; ++d) a.rho_grad[i * D + d] = g.c_g * dg[d];
-            }
-            if ((MASK & S_MOMENT) && a.moment) {
-                float *o = a.moment + i * (D * D);
-                if (D == 2) {
-                    reinterpret_cast<float4 *>(o)[0] =
-                        make_float4(g.c_g * mom[0], g.c_g * mom[1], g.c_g * mom[1], g.c_g * mom[2]);
-                } else {
-                    o[0] = g.c_g * mom[0]; o[1] = g.c_g * mom[1]; o[2] = g.c_g * mom[2];
-                    o[3] = g.c_g * mom[1]; o[4] = g.c_g * mom[3]; o[5] = g.c_g * mom[4];
-                    o[6] = g.c_g * mom[2]; o[7] = g.c_g * mom[4]; o[8] = g.c_g * mom[5];
-                }
-            }
-        }
-    }
-}
 
 // dK/dr applied to u:  J u = phi u - psi (r.u) r.
 template <int D>
@@ -121,53 +26,181 @@ __device__ inline void apply_jacobian(float phi, float psi, float rx, float ry, 
     oz = D == 3 ? phi * uz - s * rz : 0.f;
 }
 
+constexpr int kScalarLpp = 4;                // lanes per particle
+constexpr int kScalarPpw = 32 / kScalarLpp;  // particles per warp pass
+constexpr unsigned kScalarSubMask = (1u << kScalarLpp) - 1u;
+
+// One warp per work item (several warps share an item when items are scarce).  The warp handles 8
+// particles of the item per pass: each particle has a sub-group of 4 lanes that split its
+// candidates, every lane adds the contribution of its own accepted pair, and a sub-group shuffle
+// reduction yields the sums.  Eight independent particles per warp keep many loads in flight.
+// The sweep can record the accepted pairs of each particle (in candidate order) in the
+// neighbour-list cache for the sweeps that follow.
+template <int D, bool PER, int MASK>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
+    __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int4 *rng = s_ranges[warp];
+    const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
+    constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
+    constexpr bool kPoly = (MASK & S_DENSITY) != 0;
+    constexpr int kSym = D * (D + 1) / 2;
+    const int K = a.pair_stride;
+
+    const int vrows = g.max_blocks * g.split;
+    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+        const int row = vrow / g.split, part = vrow - row * g.split;
+        const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+        if (it.count <= 0) break;  // rows after the last work item are zero
+        if (part * kScalarPpw >= it.count) continue;
+        __syncwarp();
+        const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+
+        for (int k0 = part * kScalarPpw; k0 < it.count; k0 += g.split * kScalarPpw) {
+            const int k = k0 + sub;
+            const bool ivalid = k < it.count;
+            const long long i = it.first + (ivalid ? k : 0);
+            const Pos<D> pi = load_pos<D>(a.x, i);
+            int32_t *list = a.pair_cache ? a.pair_cache + i * K + 1 : nullptr;
+            float cnt = 0.f, rho = 0.f, dg[3] = {0.f, 0.f, 0.f}, mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            int listed = 0;
+            for (int r = 0; r < nr; ++r) {
+                const int4 rg = rng[r];
+                const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
+                for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
+                    const int j = j0 + sl;
+                    float rx = 0.f, ry = 0.f, rz = 0.f, q = 0.f;
+                    bool acc = false;
+                    if (ivalid && j < rg.y) {
+                        const Pos<D> pj = load_pos<D>(a.x, j);
+                        q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
+                        acc = q < g.h2;
+                    }
+                    if (list) {  // warp-uniform
+                        const unsigned bits = (__ballot_sync(kFull, acc) >> (sub * kScalarLpp)) & kScalarSubMask;
+                        const int pos = listed + __popc(bits & ((1u << sl) - 1u));
+                        if (acc && pos < K - 1) list[pos] = j;
+                        listed += __popc(bits);
+                    }
+                    if (!acc) continue;
+                    if (MASK & S_COUNT) cnt += 1.0f;
+                    const float mj = (kPoly || kSpiky) ? (a.mass ? __ldg(a.mass + j) : 1.0f) : 0.f;
+                    if (kPoly) {
+                        const float t = fmaxf(g.h2 - q, 0.f);
+                        rho = fmaf(mj, t * t * t, rho);
+                    }
+                    if (kSpiky && q > 0.f) {
+                        float d;
+                        const float phi = spiky_phi(q, g.h, d);
+                        if (MASK & S_DGRAD) {
+                            const float w = mj * phi;
+                            dg[0] = fmaf(w, rx, dg[0]);
+                            dg[1] = fmaf(w, ry, dg[1]);
+                            if (D == 3) dg[2] = fmaf(w, rz, dg[2]);
+                        }
+                        if (MASK & S_MOMENT) {
+                            const float w = phi * mj / __ldg(a.rho_in + j);
+                            mom[0] = fmaf(w * rx, rx, mom[0]);
+                            mom[1] = fmaf(w * rx, ry, mom[1]);
+                            if (D == 2) {
+                                mom[2] = fmaf(w * ry, ry, mom[2]);
+                            } else {
+                                mom[2] = fmaf(w * rx, rz, mom[2]);
+                                mom[3] = fmaf(w * ry, ry, mom[3]);
+                                mom[4] = fmaf(w * ry, rz, mom[4]);
+                                mom[5] = fmaf(w * rz, rz, mom[5]);
+                            }
+                        }
+                    }
+                }
+            }
+            if (MASK & S_COUNT) cnt = subgroup_sum<kScalarLpp>(cnt);
+            if (kPoly) rho = subgroup_sum<kScalarLpp>(rho);
+            if (MASK & S_DGRAD) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) dg[d] = subgroup_sum<kScalarLpp>(dg[d]);
+            }
+            if (MASK & S_MOMENT) {
+#pragma unroll
+                for (int d = 0; d < kSym; ++d) mom[d] = subgroup_sum<kScalarLpp>(mom[d]);
+            }
+            if (ivalid && sl == 0) {
+                if (list) list[-1] = listed <= K - 1 ? listed : -1;
+                if ((MASK & S_COUNT) && a.count) a.count[i] = cnt;
+                if (kPoly && a.rho_out) a.rho_out[i] = g.c_s * rho;
+                if ((MASK & S_DGRAD) && a.rho_grad) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) a.rho_grad[i * D + d] = g.c_g * dg[d];
+                }
+                if ((MASK & S_MOMENT) && a.moment) {
+                    float *o = a.moment + i * (D * D);
+                    if (D == 2) {
+                        reinterpret_cast<float4 *>(o)[0] =
+                            make_float4(g.c_g * mom[0], g.c_g * mom[1], g.c_g * mom[1], g.c_g * mom[2]);
+                    } else {
+                        o[0] = g.c_g * mom[0]; o[1] = g.c_g * mom[1]; o[2] = g.c_g * mom[2];
+                        o[3] = g.c_g * mom[1]; o[4] = g.c_g * mom[3]; o[5] = g.c_g * mom[4];
+                        o[6] = g.c_g * mom[2]; o[7] = g.c_g * mom[4]; o[8] = g.c_g * mom[5];
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Gather backward of density / density gradient / moment matrix, same layout (8 particles per warp
+// pass, 4 lanes each).  With a neighbour-list cache of the snapshot the lanes of a sub-group walk
+// the list of their particle; particles without a list (cache off, or more neighbours than the
+// list holds) test the candidates of the cells.
 template <int D, bool PER, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
     __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kWarpsPerCta + warp;
-    if (row >= g.max_blocks) return;
-    const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
-    if (it.count <= 0) return;
     int4 *rng = s_ranges[warp];
-    const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
     const int sub = lane / kScalarLpp, sl = lane % kScalarLpp;
     constexpr bool kSpiky = (MASK & (S_DGRAD | S_MOMENT)) != 0;
     constexpr int DD = D * D;
+    const int K = a.pair_stride;
 
-    for (int k0 = 0; k0 < it.count; k0 += kScalarPpw) {
-        const int k = k0 + sub;
-        const bool ivalid = k < it.count;
-        const long long i = it.first + (ivalid ? k : 0);
-        const Pos<D> pi = load_pos<D>(a.x, i);
-        const float mi = a.mass ? __ldg(a.mass + i) : 1.0f;
-        float gri = 0.f, gdi[3] = {0.f, 0.f, 0.f}, gmi[DD], vi = 0.f;
-        if (MASK & S_DENSITY) {
-            if (a.g_rho_a) gri += __ldg(a.g_rho_a + i);
-            if (a.g_rho_b) gri += __ldg(a.g_rho_b + i);
-        }
-        if (MASK & S_DGRAD)
+    const int vrows = g.max_blocks * g.split;
+    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+        const int row = vrow / g.split, part = vrow - row * g.split;
+        const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
+        if (it.count <= 0) break;
+        if (part * kScalarPpw >= it.count) continue;
+        __syncwarp();
+        const int nr = build_ranges<D>(g, a.bin_offsets, it, rng);
+
+        for (int k0 = part * kScalarPpw; k0 < it.count; k0 += g.split * kScalarPpw) {
+            const int k = k0 + sub;
+            const bool ivalid = k < it.count;
+            const long long i = it.first + (ivalid ? k : 0);
+            const Pos<D> pi = load_pos<D>(a.x, i);
+            const float mi = a.mass ? __ldg(a.mass + i) : 1.0f;
+            float gri = 0.f, gdi[3] = {0.f, 0.f, 0.f}, gmi[DD], vi = 0.f;
+            if (MASK & S_DENSITY) {
+                if (a.g_rho_a) gri += __ldg(a.g_rho_a + i);
+                if (a.g_rho_b) gri += __ldg(a.g_rho_b + i);
+            }
+            if (MASK & S_DGRAD) {
 #pragma unroll
-            for (int d = 0; d < D; ++d) gdi[d] = __ldg(a.g_rho_grad + i * D + d);
-        if (MASK & S_MOMENT) {
+                for (int d = 0; d < D; ++d) gdi[d] = __ldg(a.g_rho_grad + i * D + d);
+            }
+            if (MASK & S_MOMENT) {
 #pragma unroll
-            for (int d = 0; d < DD; ++d) gmi[d] = __ldg(a.g_moment + i * DD + d);
-            vi = mi / __ldg(a.rho_in + i);
-        }
-        float dxs[3] = {0.f, 0.f, 0.f};  // poly6 part, scaled by c_s at the end
-        float dxg[3] = {0.f, 0.f, 0.f};  // spiky part, scaled by c_g at the end
-        float drho = 0.f;
-        for (int r = 0; r < nr; ++r) {
-            const int4 rg = rng[r];
-            const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
-            for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
-                const long long j = j0 + sl;
-                if (!(ivalid && j < rg.y)) continue;
-                const Pos<D> pj = load_pos<D>(a.x, j);
-                float rv[3];
-                const float q = displacement<D, PER>(g, org, pj.x, pj.y, pj.z, rv[0], rv[1], rv[2]);
-                if (!(q < g.h2) || !(q > 0.f)) continue;  // the self / coincident pair has zero gradient
+                for (int d = 0; d < DD; ++d) gmi[d] = __ldg(a.g_moment + i * DD + d);
+                vi = mi / __ldg(a.rho_in + i);
+            }
+            float dxs[3] = {0.f, 0.f, 0.f};  // poly6 part, scaled by c_s at the end
+            float dxg[3] = {0.f, 0.f, 0.f};  // spiky part, scaled by c_g at the end
+            float drho = 0.f;
+
+            // contribution of one pair (the self / coincident pair has zero gradient)
+            auto visit = [&](long long j, float rx, float ry, float rz, float q) {
+                if (!(q > 0.f)) return;
+                const float rv[3] = {rx, ry, rz};
                 const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                 if (MASK & S_DENSITY) {
                     float grj = 0.f;
@@ -213,47 +246,82 @@ scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
                         drho = fmaf(rr, phi, drho);
                     }
                 }
-            }
-        }
-        float out[3];
-#pragma unroll
-        for (int d = 0; d < D; ++d)
-            out[d] = subgroup_sum<kScalarLpp>(g.c_s * dxs[d] + g.c_g * dxg[d]);
-        if (MASK & S_MOMENT) drho = subgroup_sum<kScalarLpp>(drho);
-        if (ivalid && sl == 0) {
-            if (a.grad_x) {
-                if (D == 2) {
-                    float2 *o = reinterpret_cast<float2 *>(a.grad_x) + i;
-                    float2 v = make_float2(out[0], out[1]);
-                    if (a.accumulate_x) { const float2 p = *o; v.x += p.x; v.y += p.y; }
-                    *o = v;
-                } else {
-                    float4 *o = reinterpret_cast<float4 *>(a.grad_x) + i;
-                    float4 v = make_float4(out[0], out[1], out[2], 0.f);
-                    if (a.accumulate_x) { const float4 p = *o; v.x += p.x; v.y += p.y; v.z += p.z; }
-                    *o = v;
+            };
+
+            int listed = -1;  // the same in the four lanes of a sub-group
+            if (a.pair_cache && ivalid) listed = __ldg(a.pair_cache + i * K);
+            if (listed >= 0) {
+                const int32_t *list = a.pair_cache + i * K + 1;
+                for (int e = sl; e < listed; e += kScalarLpp) {
+                    const int j = __ldg(list + e);
+                    const Pos<D> pj = load_pos<D>(a.x, j);
+                    float rx, ry, rz;
+                    listed_displacement<D, PER>(g, pi, pj, rx, ry, rz);
+                    visit(j, rx, ry, rz, sq_norm_fast<D>(rx, ry, rz));
                 }
             }
-            if ((MASK & S_MOMENT) && a.grad_rho) a.grad_rho[i] = -g.c_g * (vi * vi / mi) * drho;
+            if (__any_sync(kFull, ivalid && listed < 0)) {
+                for (int r = 0; r < nr; ++r) {
+                    const int4 rg = rng[r];
+                    const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
+                    for (int j0 = rg.x; j0 < rg.y; j0 += kScalarLpp) {
+                        const int j = j0 + sl;
+                        if (!(ivalid && listed < 0 && j < rg.y)) continue;
+                        const Pos<D> pj = load_pos<D>(a.x, j);
+                        float rx, ry, rz;
+                        const float q = displacement<D, PER, false>(g, org, pj.x, pj.y, pj.z, rx, ry, rz);
+                        if (q < g.h2) visit(j, rx, ry, rz, q);
+                    }
+                }
+            }
+
+            float out[3];
+#pragma unroll
+            for (int d = 0; d < D; ++d) out[d] = subgroup_sum<kScalarLpp>(g.c_s * dxs[d] + g.c_g * dxg[d]);
+            if (MASK & S_MOMENT) drho = subgroup_sum<kScalarLpp>(drho);
+            if (ivalid && sl == 0) {
+                if (a.grad_x) {
+                    if (D == 2) {
+                        float2 *o = reinterpret_cast<float2 *>(a.grad_x) + i;
+                        float2 v = make_float2(out[0], out[1]);
+                        if (a.accumulate_x) { const float2 p = *o; v.x += p.x; v.y += p.y; }
+                        *o = v;
+                    } else {
+                        float4 *o = reinterpret_cast<float4 *>(a.grad_x) + i;
+                        float4 v = make_float4(out[0], out[1], out[2], 0.f);
+                        if (a.accumulate_x) { const float4 p = *o; v.x += p.x; v.y += p.y; v.z += p.z; }
+                        *o = v;
+                    }
+                }
+                if ((MASK & S_MOMENT) && a.grad_rho) a.grad_rho[i] = -g.c_g * (vi * vi / mi) * drho;
+            }
         }
     }
 }
 
 // ---------------------------------------------------------------------------
-// dispatch
+// dispatch: persistent launches (every SM filled to the kernel's occupancy)
 // ---------------------------------------------------------------------------
+template <typename Kernel, typename Args>
+static int launch_persistent(const Geom &g, Kernel kernel, const Args &a, cudaStream_t st, const char *what) {
+    const int threads = kWarpsPerCta * 32;
+    int ctas = 0;
+    int rc = persistent_ctas(kernel, threads, 0, &ctas);
+    if (rc != NPA_OK) return rc;
+    const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
+    kernel<<<needed < ctas ? needed : ctas, threads, 0, st>>>(a, g);
+    return check_launch(what);
+}
+
 template <int MASK>
 static int launch_scalar_fwd_mask(const Geom &g, const ScalarFwdArgs &a, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
-    const unsigned threads = kWarpsPerCta * 32;
+    const char *what = "scalar_forward_kernel";
     if (g.dim == 2) {
-        if (g.periodic) scalar_forward_kernel<2, true, MASK><<<blocks, threads, 0, st>>>(a, g);
-        else scalar_forward_kernel<2, false, MASK><<<blocks, threads, 0, st>>>(a, g);
-    } else {
-        if (g.periodic) scalar_forward_kernel<3, true, MASK><<<blocks, threads, 0, st>>>(a, g);
-        else scalar_forward_kernel<3, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+        if (g.periodic) return launch_persistent(g, scalar_forward_kernel<2, true, MASK>, a, st, what);
+        return launch_persistent(g, scalar_forward_kernel<2, false, MASK>, a, st, what);
     }
-    return check_launch("scalar_forward_kernel");
+    if (g.periodic) return launch_persistent(g, scalar_forward_kernel<3, true, MASK>, a, st, what);
+    return launch_persistent(g, scalar_forward_kernel<3, false, MASK>, a, st, what);
 }
 
 int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st) {
@@ -272,16 +340,13 @@ int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaS
 
 template <int MASK>
 static int launch_scalar_bwd_mask(const Geom &g, const ScalarBwdArgs &a, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((g.max_blocks + kWarpsPerCta - 1) / kWarpsPerCta);
-    const unsigned threads = kWarpsPerCta * 32;
+    const char *what = "scalar_backward_kernel";
     if (g.dim == 2) {
-        if (g.periodic) scalar_backward_kernel<2, true, MASK><<<blocks, threads, 0, st>>>(a, g);
-        else scalar_backward_kernel<2, false, MASK><<<blocks, threads, 0, st>>>(a, g);
-    } else {
-        if (g.periodic) scalar_backward_kernel<3, true, MASK><<<blocks, threads, 0, st>>>(a, g);
-        else scalar_backward_kernel<3, false, MASK><<<blocks, threads, 0, st>>>(a, g);
+        if (g.periodic) return launch_persistent(g, scalar_backward_kernel<2, true, MASK>, a, st, what);
+        return launch_persistent(g, scalar_backward_kernel<2, false, MASK>, a, st, what);
     }
-    return check_launch("scalar_backward_kernel");
+    if (g.periodic) return launch_persistent(g, scalar_backward_kernel<3, true, MASK>, a, st, what);
+    return launch_persistent(g, scalar_backward_kernel<3, false, MASK>, a, st, what);
 }
 
 int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st) {

@@ -181,13 +181,14 @@ class DensityPair(torch.autograd.Function):
     """density and density_gradient of the same positions in one sweep."""
 
     @staticmethod
-    def forward(ctx, x_bin, mass, snapshot):
+    def forward(ctx, x_bin, mass, snapshot, pairs=None):
         B, N = x_bin.shape[:2]
         rho = torch.empty(B, N, dtype=torch.float32, device=x_bin.device)
         rho_grad = torch.empty(B, N, snapshot.dim, dtype=torch.float32, device=x_bin.device)
         snapshot.grid.perception_forward(x_bin, mass, None, rho, None, rho_grad, None, None, None,
-                                         snapshot.bin_offsets, snapshot.block_info)
+                                         snapshot.bin_offsets, snapshot.block_info, pair_cache=pairs)
         ctx.save_for_backward(x_bin, *([] if mass is None else [mass]))
+        ctx.pairs = pairs
         ctx.has_mass = mass is not None
         ctx.snapshot = snapshot
         ctx.dLdx = x_bin.requires_grad
@@ -196,30 +197,32 @@ class DensityPair(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_rho, g_rho_grad):
         if not ctx.dLdx or (g_rho is None and g_rho_grad is None):
-            return None, None, None
+            return None, None, None, None
         saved = ctx.saved_tensors
         x_bin, mass = saved[0], (saved[1] if ctx.has_mass else None)
         snap = ctx.snapshot
         grad_x = torch.empty_like(x_bin)
         cont = lambda t: None if t is None else t.contiguous()
         snap.grid.density_chain_backward(x_bin, mass, cont(g_rho), None, cont(g_rho_grad), grad_x, False,
-                                         snap.bin_offsets, snap.block_info)
-        return grad_x, None, None
+                                         snap.bin_offsets, snap.block_info, pair_cache=ctx.pairs)
+        return grad_x, None, None, None
 
 
 class BlurGradient(torch.autograd.Function):
     """blur, feature gradient and (not differentiated) moment matrix in one sweep."""
 
     @staticmethod
-    def forward(ctx, x_bin, s_bin, rho, mass, snapshot):
+    def forward(ctx, x_bin, s_bin, rho, mass, snapshot, pairs=None):
         B, N, C = s_bin.shape
         dev, dim = x_bin.device, snapshot.dim
         s_blur = torch.empty_like(s_bin)
         s_grad = torch.empty(B, N, C, dim, dtype=torch.float32, device=dev)
         moment = torch.empty(B, N, dim, dim, dtype=torch.float32, device=dev)
-        pairs = _new_pair_cache(s_bin, x_bin.requires_grad or s_bin.requires_grad or rho.requires_grad)
+        valid = pairs is not None          # lists recorded by the density sweep of the same positions
+        if pairs is None:
+            pairs = _new_pair_cache(s_bin, x_bin.requires_grad or s_bin.requires_grad or rho.requires_grad)
         snapshot.grid.blur_gradient_forward(x_bin, rho, mass, s_bin, s_blur, s_grad, snapshot.bin_offsets,
-                                            snapshot.block_info, moment, pair_cache=pairs)
+                                            snapshot.block_info, moment, pair_cache=pairs, pair_cache_valid=valid)
         ctx.save_for_backward(x_bin, s_bin, rho, *([] if mass is None else [mass]))
         ctx.pairs = pairs
         ctx.has_mass = mass is not None
@@ -235,7 +238,7 @@ class BlurGradient(torch.autograd.Function):
         mass = saved[3] if ctx.has_mass else None
         dLdx, dLds, dLdrho = ctx.needs
         if (g_blur is None and g_grad is None) or not (dLdx or dLds or dLdrho):
-            return None, None, None, None, None
+            return None, None, None, None, None, None
         snap = ctx.snapshot
         cont = lambda t: None if t is None else t.contiguous()
         grad_x = torch.empty_like(x_bin) if dLdx else None
@@ -243,7 +246,7 @@ class BlurGradient(torch.autograd.Function):
         grad_rho = torch.empty_like(rho) if dLdrho else None
         snap.grid.blur_gradient_backward(x_bin, rho, mass, s_bin, cont(g_blur), cont(g_grad), grad_x, grad_s,
                                          grad_rho, snap.bin_offsets, snap.block_info, pair_cache=ctx.pairs)
-        return grad_x, grad_s, grad_rho, None, None
+        return grad_x, grad_s, grad_rho, None, None, None
 
 
 def _zeros_like_shape(shape, dtype, device):
@@ -328,8 +331,12 @@ class Density(torch.autograd.Function):
 
 def density(x_bin, snapshot, mass=None):
     if _FUSION["enabled"]:
-        rho, rho_grad = DensityPair.apply(x_bin, None if mass is None else _default_mass(x_bin, mass), snapshot)
+        pairs = _new_pair_cache(x_bin, True)
+        rho, rho_grad = DensityPair.apply(x_bin, None if mass is None else _default_mass(x_bin, mass), snapshot,
+                                          pairs)
         _park(snapshot, "density_gradient", _key(x_bin, mass), rho_grad)
+        if pairs is not None:
+            _park(snapshot, "pair_cache", _key(x_bin), pairs)   # the lists depend on the positions only
         return rho
     return Density.apply(x_bin, _default_mass(x_bin, mass), snapshot)
 
@@ -370,7 +377,8 @@ class Blur(_FeatureOp):
 def blur(x_bin, rho, s_bin, snapshot, mass=None):
     if _FUSION["enabled"]:
         s_blur, s_grad, moment = BlurGradient.apply(
-            x_bin, s_bin, rho, None if mass is None else _default_mass(x_bin, mass), snapshot)
+            x_bin, s_bin, rho, None if mass is None else _default_mass(x_bin, mass), snapshot,
+            _claim(snapshot, "pair_cache", x_bin))
         _park(snapshot, "gradient", _key(x_bin, rho, s_bin, mass), s_grad)
         _park(snapshot, "moment_matrix", _key(x_bin, rho, mass), moment)
         return s_blur

@@ -310,7 +310,7 @@ class _HashGridBase:
 
     # ---- fused sweeps (no counterpart in the reference module) ------------------
     def blur_gradient_forward(self, binned_positions, rho, mass, state_in, state_out, state_gradient_out,
-                              bin_offsets, block_info, moment_matrix_out=None, pair_cache=None):
+                              bin_offsets, block_info, moment_matrix_out=None, pair_cache=None, pair_cache_valid=False):
         """blur and gradient in one launch; ``mass`` and either output may be None.  With
         ``moment_matrix_out`` (and both other outputs) the moment matrix rides the same sweep."""
         C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
@@ -330,7 +330,8 @@ class _HashGridBase:
             return
         self._call(_lib.npa_blur_gradient_forward, binned_positions, self._ref(), C, N.ptr(binned_positions),
                    N.ptr(rho), N.ptr(mass), N.ptr(state_in), N.ptr(state_out), N.ptr(state_gradient_out),
-                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
+                   N.ptr(moment_matrix_out), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache),
+                   1 if pair_cache_valid else 0)
 
     def blur_gradient_backward(self, binned_positions, rho, mass, state_in, dL_blur_state_out, dL_grad_state_out,
                                grad_x, grad_s, grad_rho, bin_offsets, block_info, pair_cache=None):
@@ -360,7 +361,7 @@ class _HashGridBase:
                    *self._pairs(pair_cache))
 
     def density_chain_backward(self, binned_positions, mass, dL_rho_a, dL_rho_b, dL_density_gradient_out, grad_x,
-                               accumulate, bin_offsets, block_info):
+                               accumulate, bin_offsets, block_info, pair_cache=None):
         """density (+ density gradient) backward; the two rho upstreams are summed."""
         self._pos(binned_positions, "binned_positions")
         if mass is not None:
@@ -375,7 +376,7 @@ class _HashGridBase:
         self._snap(bin_offsets, block_info)
         self._call(_lib.npa_density_chain_backward, binned_positions, self._ref(), N.ptr(binned_positions),
                    N.ptr(mass), N.ptr(dL_rho_a), N.ptr(dL_rho_b), N.ptr(dL_density_gradient_out), N.ptr(grad_x),
-                   1 if accumulate else 0, N.ptr(bin_offsets), N.ptr(block_info))
+                   1 if accumulate else 0, N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
     # ---- packed perception (no counterpart in the reference module) ------------
     def perceive_features_forward(self, binned_positions, mass, state_in, coef, dg_scale, inv_tol, log_norm_grad,
