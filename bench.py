@@ -204,6 +204,24 @@ def bytes_per_particle(w):
     }
 
 
+def backward_flops_per_pair(w):
+    """fp32 operations the fused blur+gradient backward spends on one accepted pair (a multiply-add
+    counts 2): per feature 3 multiply-adds of the blur terms and, per axis, 5 of the gradient terms
+    (h = v_j gG_i + v_i gG_j, K.h, df h, gG_j.K) plus 3 adds; per pair ~60 for the kernel scalars
+    (r^2, poly6 and spiky factors, v_j = m_j / rho_j) and the position terms."""
+    C, D = w.C, w.dim
+    return C * (2 * 3 + 2 * 5 * D + 3) + 60
+
+
+def fp32_roofline(w, accepted_pairs, launch_ms, clocks):
+    sm_mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
+    peak = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
+    achieved = accepted_pairs * backward_flops_per_pair(w) / (launch_ms * 1e-3) / 1e12
+    return {"bound": "fp32", "kernel": "feature_backward_kernel", "achieved": achieved, "peak": peak,
+            "unit": "TFLOP/s", "frac": achieved / peak, "accepted_pairs": accepted_pairs,
+            "flops_per_pair": backward_flops_per_pair(w)}
+
+
 def run_gpu_arm(args, w):
     import torch
     import torch.distributed as dist
@@ -290,6 +308,10 @@ def run_gpu_arm(args, w):
     clocks = sampler.stop() if rank == 0 else None
 
     phase_ms = {p: sum(e[i].elapsed_time(e[i + 1]) for e in events) / args.steps for i, p in enumerate(phases)}
+    # accepted pairs (r < h, self pair included) of this rank's systems, for the arithmetic model below
+    cnt = torch.empty(B, N, **f32)
+    hg.count_forward(x_bin, cnt, offs, info)
+    accepted_pairs = float(cnt.sum(dtype=torch.float64).item())
     step_ms_local = sum(e[0].elapsed_time(e[6]) for e in events) / args.steps
     t = torch.tensor([step_ms_local], dtype=torch.float64, device=dev)
     if world > 1:
@@ -348,6 +370,10 @@ def run_gpu_arm(args, w):
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                          "algorithmic_bytes_per_launch": B * N * bpp[dom], "launch_ms": phase_ms[dom]},
+            # secondary ceiling: fp32 multiply-adds of the dominant kernel against the FMA pipes
+            # (148 SMs x 128 lanes x 2 flop x max SM clock); the count of operations per accepted
+            # pair is the kernel's own arithmetic (see backward_flops_per_pair)
+            "fp32_roofline": fp32_roofline(w, accepted_pairs, phase_ms[dom], clocks),
             "step_roofline": {"algorithmic_bytes_per_particle": sum(bpp.values()),
                               "achieved": B * N * sum(bpp.values()) / (step_ms_local * 1e-3) / 1e9,
                               "frac": B * N * sum(bpp.values()) / (step_ms_local * 1e-3) / 1e9 / peak},

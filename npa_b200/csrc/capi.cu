@@ -54,6 +54,34 @@ int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *
     return NPA_OK;
 }
 
+constexpr int kTicketSlots = 1024;  // first half: eager launches; second half: launches under stream capture
+static __device__ unsigned int g_row_tickets[kTicketSlots * 2];  // zero at load; every launch leaves its words zero
+
+int acquire_row_tickets(cudaStream_t st, unsigned int **out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static unsigned int *base[kMaxDevices] = {nullptr};
+    static unsigned int next[2] = {0u, 0u};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(NPA_ERR_UNSUPPORTED, "device ordinal %d is out of range", dev);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(st, &cap);
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaStreamIsCapturing: %s", cudaGetErrorString(e));
+    const int half = cap == cudaStreamCaptureStatusNone ? 0 : 1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!base[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_row_tickets);
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetSymbolAddress(row tickets): %s", cudaGetErrorString(e));
+        base[dev] = static_cast<unsigned int *>(p);
+    }
+    const unsigned int slot = half * (kTicketSlots / 2) + next[half]++ % (kTicketSlots / 2);
+    *out = base[dev] + 2 * slot;
+    return NPA_OK;
+}
+
 // Common checks of an operator call: geometry, the two snapshot arrays, the
 // positions and their vector alignment.
 static int begin_op(const char *name, const npa_grid *gd, Geom *g, const float *x,

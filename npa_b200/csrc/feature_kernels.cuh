@@ -158,7 +158,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     // persistent warps: consecutive rows go to the warps of one CTA, then to the next CTA
     // g.split warps share one row (its particles are dealt round-robin) when rows are scarce
     const int vrows = g.max_blocks * g.split;
-    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    for (int vrow = next_row(a.tickets); vrow < vrows; vrow = next_row(a.tickets)) {
     const int row = vrow / g.split, part = vrow - row * g.split;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) break;  // rows after the last work item are zero
@@ -360,6 +360,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
         }
     }
     }  // rows
+    release_rows(a.tickets);
 }
 
 template <int D, bool PER, int LPP, int VW, int MASK, bool FULL>
@@ -387,7 +388,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
 
     // g.split warps share one row (its particles are dealt round-robin) when rows are scarce
     const int vrows = g.max_blocks * g.split;
-    for (int vrow = blockIdx.x * WB + warp; vrow < vrows; vrow += gridDim.x * WB) {
+    for (int vrow = next_row(a.tickets); vrow < vrows; vrow = next_row(a.tickets)) {
     const int row = vrow / g.split, part = vrow - row * g.split;
     const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
     if (it.count <= 0) break;  // rows after the last work item are zero
@@ -619,6 +620,7 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
         }
     }
     }  // rows
+    release_rows(a.tickets);
 }
 
 // ---------------------------------------------------------------------------
@@ -640,7 +642,9 @@ int launch_feature_forward_mask(const Geom &g, Kernel kernel, const FeatureFwdAr
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
     const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
-    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
+    FeatureFwdArgs b = a;
+    if ((rc = acquire_row_tickets(st, &b.tickets)) != NPA_OK) return rc;
+    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(b, g);
     return check_launch("feature_forward_kernel");
 }
 
@@ -687,7 +691,9 @@ int launch_feature_backward_mask(const Geom &g, Kernel kernel, const FeatureBwdA
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
     const int needed = (g.max_blocks * g.split + WB - 1) / WB;
-    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(a, g);
+    FeatureBwdArgs b = a;
+    if ((rc = acquire_row_tickets(st, &b.tickets)) != NPA_OK) return rc;
+    kernel<<<needed < ctas ? needed : ctas, threads, dyn, st>>>(b, g);
     return check_launch("feature_backward_kernel");
 }
 

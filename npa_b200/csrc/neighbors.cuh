@@ -34,6 +34,29 @@ __device__ inline WorkItem load_item(const int32_t *__restrict__ block_info,
     return it;
 }
 
+// Dynamic distribution of work-list rows over the resident warps of a persistent launch.
+// `tickets` points at two words that are zero when the launch starts: [0] the next row to hand
+// out, [1] the number of CTAs that have finished.  A warp draws rows until they run out; rows
+// come out in cell order, so warps running at the same time work on neighbouring cells.  The
+// last CTA to finish puts both words back to zero for the next launch that uses them.
+__device__ inline int next_row(unsigned int *tickets) {
+    int row = 0;
+    if ((threadIdx.x & 31) == 0) row = (int)atomicAdd(tickets, 1u);
+    return __shfl_sync(kFull, row, 0);
+}
+
+// Called by every thread of the CTA once its warps will draw no more rows.
+__device__ inline void release_rows(unsigned int *tickets) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int done = atomicAdd(tickets + 1, 1u);
+        if (done == gridDim.x - 1) {  // every other CTA has drawn its last row before it counted itself
+            tickets[0] = 0u;
+            tickets[1] = 0u;
+        }
+    }
+}
+
 // Neighbour coordinate along one axis; false when the clamped grid ends there
 // or when a small periodic axis would visit the same cell twice.  `shift` is
 // the periodic image the neighbour cell lies in relative to cell c: -1 when the

@@ -25,6 +25,7 @@ struct ScalarFwdArgs {
     const int32_t *block_info;
     int32_t *pair_cache;  // neighbour lists to write ([B*N, pair_stride]) or NULL
     int pair_stride;
+    unsigned int *tickets;  // row tickets of this launch (set by the launcher)
 };
 
 struct ScalarBwdArgs {
@@ -42,6 +43,7 @@ struct ScalarBwdArgs {
     const int32_t *block_info;
     const int32_t *pair_cache;  // neighbour lists of this snapshot to read, or NULL
     int pair_stride;
+    unsigned int *tickets;  // row tickets of this launch (set by the launcher)
 };
 
 struct FeatureFwdArgs {
@@ -67,6 +69,7 @@ struct FeatureFwdArgs {
     int32_t *pair_cache;     // [B*N, pair_stride] or NULL
     int pair_stride;
     int pair_cache_valid;    // 0: this sweep writes the lists; 1: they are valid, read them instead of searching
+    unsigned int *tickets;  // row tickets of this launch (set by the launcher)
 };
 
 struct FeatureBwdArgs {
@@ -84,6 +87,7 @@ struct FeatureBwdArgs {
     const int32_t *block_info;
     const int32_t *pair_cache;  // neighbour lists written by the forward sweep of the same snapshot, or NULL
     int pair_stride;
+    unsigned int *tickets;  // row tickets of this launch (set by the launcher)
 };
 
 // Number of CTAs of a persistent launch of `kernel`: every SM filled to the kernel's occupancy.
@@ -94,6 +98,14 @@ template <typename Kernel>
 int persistent_ctas(Kernel kernel, int threads, size_t dyn_smem, int *out) {
     return persistent_ctas_impl(reinterpret_cast<const void *>(kernel), threads, dyn_smem, out);
 }
+
+// Two zeroed words in device memory for the row tickets of one persistent launch (next_row /
+// release_rows in neighbors.cuh).  They live in a small array inside the library, handed out round
+// robin: launches in one stream are ordered, and launches in different streams get different words
+// unless hundreds of launches lie between them.  Launches recorded into a CUDA graph draw from a
+// separate half of the array, so a replaying graph never shares words with an eager launch.
+// Defined in capi.cu.
+int acquire_row_tickets(cudaStream_t st, unsigned int **out);
 
 int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st);
 int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st);

@@ -49,7 +49,7 @@ scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
     const int K = a.pair_stride;
 
     const int vrows = g.max_blocks * g.split;
-    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    for (int vrow = next_row(a.tickets); vrow < vrows; vrow = next_row(a.tickets)) {
         const int row = vrow / g.split, part = vrow - row * g.split;
         const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
         if (it.count <= 0) break;  // rows after the last work item are zero
@@ -147,6 +147,7 @@ scalar_forward_kernel(ScalarFwdArgs a, Geom g) {
             }
         }
     }
+    release_rows(a.tickets);
 }
 
 // Gather backward of density / density gradient / moment matrix, same layout (8 particles per warp
@@ -165,7 +166,7 @@ scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
     const int K = a.pair_stride;
 
     const int vrows = g.max_blocks * g.split;
-    for (int vrow = blockIdx.x * kWarpsPerCta + warp; vrow < vrows; vrow += gridDim.x * kWarpsPerCta) {
+    for (int vrow = next_row(a.tickets); vrow < vrows; vrow = next_row(a.tickets)) {
         const int row = vrow / g.split, part = vrow - row * g.split;
         const WorkItem it = load_item(a.block_info, a.bin_offsets, row);
         if (it.count <= 0) break;
@@ -297,6 +298,7 @@ scalar_backward_kernel(ScalarBwdArgs a, Geom g) {
             }
         }
     }
+    release_rows(a.tickets);
 }
 
 // ---------------------------------------------------------------------------
@@ -309,7 +311,9 @@ static int launch_persistent(const Geom &g, Kernel kernel, const Args &a, cudaSt
     int rc = persistent_ctas(kernel, threads, 0, &ctas);
     if (rc != NPA_OK) return rc;
     const int needed = (g.max_blocks * g.split + kWarpsPerCta - 1) / kWarpsPerCta;
-    kernel<<<needed < ctas ? needed : ctas, threads, 0, st>>>(a, g);
+    Args b = a;
+    if ((rc = acquire_row_tickets(st, &b.tickets)) != NPA_OK) return rc;
+    kernel<<<needed < ctas ? needed : ctas, threads, 0, st>>>(b, g);
     return check_launch(what);
 }
 

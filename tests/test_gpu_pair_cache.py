@@ -1,0 +1,133 @@
+"""The neighbour-list cache: the density sweep records, per particle, the accepted pairs of the
+snapshot; every later sweep (blur + gradient forward, both backward sweeps) reads the list instead
+of searching the 3^D cells.  The results must not depend on whether a list exists, on its width, or
+on some particles having more neighbours than it holds."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import make_grid
+from npa_b200.workloads import Workload, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    Workload("pc3c", dim=3, B=2, N=4000, C=16, eps=0.12, grid_size=(10, 10, 10), boundary="clamped"),
+    Workload("pc2p", dim=2, B=3, N=2500, C=12, eps=0.05, grid_size=(20, 20), boundary="periodic"),
+    Workload("pc3p", dim=3, B=1, N=5000, C=32, eps=0.125, grid_size=(8, 8, 8), boundary="periodic"),
+]
+
+
+def _binned(sph, w, seed):
+    x, s, _ = make_inputs(w, seed=seed)
+    x[..., :w.dim] *= 0.98 * w.grid_size[0] * w.eps  # fill the grid's domain
+    grid = make_grid(sph, w)
+    snap = grid.instantiate(x.cuda())
+    x_bin, s_bin = sph.bin_particles(x.cuda(), s.cuda(), snap)
+    return grid, snap, x_bin.contiguous(), s_bin.contiguous()
+
+
+def _native_sequence(w, grid, snap, x_bin, s_bin, columns, ups):
+    """density sweep -> blur+gradient sweep -> both backward sweeps through the native layer, with a
+    neighbour-list cache of `columns` columns (0: none).  Returns every output and the lists."""
+    hg = grid.hashgrid
+    B, N, C, D = w.B, w.N, w.C, w.dim
+    f32 = dict(dtype=torch.float32, device="cuda")
+    rho, blur, grad = torch.empty(B, N, **f32), torch.empty(B, N, C, **f32), torch.empty(B, N, C, D, **f32)
+    gx, gs, grho = torch.empty_like(x_bin), torch.empty_like(s_bin), torch.empty(B, N, **f32)
+    pairs = torch.full((B, N, columns), -7, dtype=torch.int32, device="cuda") if columns else None
+    offs, info = snap.bin_offsets, snap.block_info
+    hg.perception_forward(x_bin, None, None, rho, None, None, None, None, None, offs, info, pair_cache=pairs)
+    hg.blur_gradient_forward(x_bin, rho, None, s_bin, blur, grad, offs, info, pair_cache=pairs,
+                             pair_cache_valid=pairs is not None)
+    hg.blur_gradient_backward(x_bin, rho, None, s_bin, ups["g_blur"], ups["g_grad"], gx, gs, grho, offs, info,
+                              pair_cache=pairs)
+    hg.density_chain_backward(x_bin, None, ups["g_rho"], grho, None, gx, True, offs, info, pair_cache=pairs)
+    torch.cuda.synchronize()
+    return dict(rho=rho, blur=blur, grad=grad, grad_x=gx, grad_s=gs, grad_rho=grho), pairs
+
+
+@pytest.mark.parametrize("w", CASES, ids=lambda w: w.name)
+def test_results_do_not_depend_on_the_cache(w):
+    from npa_b200 import sphops as sph
+    grid, snap, x_bin, s_bin = _binned(sph, w, seed=11)
+    g = torch.Generator().manual_seed(5)
+    ups = {"g_rho": torch.randn(w.B, w.N, generator=g).cuda(),
+           "g_blur": torch.randn(w.B, w.N, w.C, generator=g).cuda(),
+           "g_grad": torch.randn(w.B, w.N, w.C, w.dim, generator=g).cuda()}
+    base, _ = _native_sequence(w, grid, snap, x_bin, s_bin, 0, ups)
+    # 8 columns: almost every particle overflows (searches the cells); 24: a mix; 129: none overflows
+    for columns in (8, 24, 129):
+        got, pairs = _native_sequence(w, grid, snap, x_bin, s_bin, columns, ups)
+        for k in base:
+            scale = float(base[k].abs().max())
+            err = float((got[k] - base[k]).abs().max())
+            # same pairs in the same order; only the displacement of a listed pair on a periodic grid
+            # is rebuilt by a different (equally exact) route
+            assert err <= 2e-6 * scale, (columns, k, err, scale)
+        counts = pairs[..., 0]
+        if columns == 8:
+            assert int((counts < 0).sum()) > 0.9 * counts.numel()
+        if columns == 129:
+            assert int((counts < 0).sum()) == 0
+
+
+@pytest.mark.parametrize("w", CASES, ids=lambda w: w.name)
+def test_list_content(w):
+    """Row = [count | indices]: count equals the count operator, the indices are distinct particles of
+    the same system within the cut-off, and the particle itself is listed."""
+    from npa_b200 import sphops as sph
+    grid, snap, x_bin, s_bin = _binned(sph, w, seed=12)
+    cnt = sph.count(x_bin, snap)
+    ups = {"g_rho": torch.zeros(w.B, w.N).cuda(), "g_blur": torch.zeros(w.B, w.N, w.C).cuda(),
+           "g_grad": torch.zeros(w.B, w.N, w.C, w.dim).cuda()}
+    cnt = cnt.cpu().numpy().reshape(-1).astype(np.int64)
+    columns = int(np.median(cnt)) + 1  # about half of the particles fit
+    _, pairs = _native_sequence(w, grid, snap, x_bin, s_bin, columns, ups)
+    pairs = pairs.cpu().numpy().reshape(w.B * w.N, columns)
+    x = x_bin.cpu().numpy().reshape(w.B * w.N, -1)[:, :w.dim].astype(np.float64)
+    fits = cnt <= columns - 1
+    assert fits.any() and (~fits).any(), "the case should hold both kinds of particle"
+    np.testing.assert_array_equal(pairs[fits, 0], cnt[fits])
+    assert (pairs[~fits, 0] == -1).all()
+    L = np.array(w.grid_size[:w.dim], dtype=np.float64) * w.eps
+    rows = np.nonzero(fits)[0][:: max(1, fits.sum() // 2000)]  # a spread sample of rows
+    for i in rows:
+        js = pairs[i, 1:1 + cnt[i]]
+        assert len(set(js.tolist())) == len(js)
+        assert i in js
+        assert (js // w.N == i // w.N).all()
+        d = x[js] - x[i]
+        if w.boundary == "periodic":
+            d -= L * np.round(d / L)
+        assert (np.sum(d * d, axis=1) < (w.eps * (1 + 1e-5)) ** 2).all()
+
+
+def test_public_api_uses_and_sizes_the_cache():
+    """sphops.set_pair_cache bounds the list width of the autograd nodes; gradients are the same with
+    the default width, a narrow one and none."""
+    from npa_b200 import sphops as sph
+    w = CASES[0]
+    x, s, _ = make_inputs(w, seed=13)
+    x[..., :w.dim] *= 0.98 * w.grid_size[0] * w.eps
+    grid = make_grid(sph, w)
+    g = torch.Generator().manual_seed(6)
+    ups = [torch.randn(w.B, w.N, generator=g).cuda(), torch.randn(w.B, w.N, w.C, generator=g).cuda(),
+           torch.randn(w.B, w.N, w.C, w.dim, generator=g).cuda()]
+    grads = []
+    try:
+        for columns in (64, 6, 0):
+            sph.set_pair_cache(columns)
+            xr, sr = x.cuda().requires_grad_(True), s.cuda().requires_grad_(True)
+            snap = grid.instantiate(xr.detach())
+            xb, sb = sph.bin_particles(xr, sr, snap)
+            outs = sph.perceive(xb, sb, snap, with_density_gradient=False)
+            torch.autograd.backward(list(outs), ups)
+            grads.append((xr.grad.clone(), sr.grad.clone()))
+    finally:
+        sph.set_pair_cache(64)
+    with pytest.raises(ValueError):
+        sph.set_pair_cache(1)
+    for gx, gs in grads[1:]:
+        assert float((gx - grads[0][0]).abs().max()) <= 2e-6 * float(grads[0][0].abs().max())
+        assert float((gs - grads[0][1]).abs().max()) <= 2e-6 * float(grads[0][1].abs().max())
