@@ -1,5 +1,6 @@
 // Host-side geometry validation and error plumbing shared by every entry point
 // of the C ABI (include/npa_b200.h).
+#include <stdlib.h>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -90,12 +91,14 @@ int make_geom(const npa_grid *in, Geom *out) {
     if (max_blocks >= (1ll << 29))
         return fail(NPA_ERR_INVALID_ARGUMENT, "work list of %lld rows is too large", max_blocks);
     g.max_blocks = (int)max_blocks;
-    // Small problems have fewer work items than a B200 has warp slots (148 SMs x ~24 warps); the
-    // feature kernels then let up to 8 warps share the particles of one item.
+    // Warps sharing a work item (its particles are dealt round-robin).  Small problems have fewer
+    // items than a B200 has warp slots (148 SMs x ~24 warps): up to 8 warps share one.  Large ones
+    // still use 2 when items can be big, so that the last rows handed out are short.
     {
         long long items = (long long)in->batch * (cells < in->particles ? cells : in->particles);
         long long split = (2ll * 148 * 24) / (items > 0 ? items : 1);
-        g.split = (int)(split < 1 ? 1 : (split > 8 ? 8 : split));
+        const long long least = in->max_particles_per_block > 8 ? 2 : 1;
+        g.split = (int)(split < least ? least : (split > 8 ? 8 : split));
     }
 
     const float eps_f = (float)in->eps;
