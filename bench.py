@@ -391,7 +391,7 @@ def run_gpu_arm(args, w):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on the
 # headline workload, from an ncu capture (profiles/); None until measured.
-TRAFFIC_BYTES_PER_LAUNCH = 239.6e6  # profiles/ncu_feature_kernels_cfg4_3d_splat.md, same workload, full launch
+TRAFFIC_BYTES_PER_LAUNCH = 273.1e6  # profiles/ncu_feature_kernels_cfg4_3d_splat.md, same workload, full launch
 
 
 def main():
