@@ -12,8 +12,12 @@
  *    input and written as 0 on output), as in the reference
  *    (sphops/utils.cuh:14-111, sph_cuda.cu:1898).
  *  - Inputs are const, outputs and scratch are caller-allocated; the library
- *    allocates nothing, never synchronises and keeps no state between calls
- *    except the thread-local text returned by npa_last_error().
+ *    allocates nothing and never synchronises.  What it keeps between calls:
+ *    the thread-local text returned by npa_last_error(), per-device launch
+ *    sizes, and a small device array of row-ticket counters that its sweep
+ *    kernels draw work from (two words per launch, zero again when the launch
+ *    ends).  The first call of an operator on a device queries those once:
+ *    make it before any stream capture.
  *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
  *  - Return value: NPA_OK (0) or a negative npa_status; on error nothing has
  *    been launched.  No C++ exception crosses this boundary.
