@@ -359,6 +359,27 @@ int npa_perceive_features_backward(const npa_grid *g, int32_t channels, const fl
                                    const int32_t *bin_offsets, const int32_t *block_info,
                                    const int32_t *pair_cache, int32_t pair_stride, void *stream);
 
+/* ---- the Euler update after perception and the per-particle MLP ----------------- *
+ * Replaces the elementwise torch code of NPA.forward (models/npa.py:145-153, the
+ * displacement limiter) and of step_euler (models/npa.py:183-203) and, with
+ * wrap != 0 on a periodic grid, HashGrid.wrap_positions (sphops/sph.py:107-123).
+ *   y [B,N,D+C]   MLP output in cell order: D raw displacement columns, C state updates
+ *   dx = alpha * y[:D] * eps / (1 + |y[:D]|)           (eps = the grid's cell size)
+ *   x_out = x_bin + dt * dx * mask      (P columns; the 3D padding column is copied)
+ *   s_out = s_bin + dt * y[D:] * mask
+ * mask [B,N] holds 0 / 1 per particle (the reference draws rand < update_prob), NULL = all
+ * ones.  The reference's optional position noise is not part of this call. */
+int npa_step_update_forward(const npa_grid *g, const float *y, const float *x_bin, const float *s_bin,
+                            const float *mask, int32_t channels, float alpha, float dt, int32_t wrap,
+                            float *x_out, float *s_out, void *stream);
+
+/* dL/dy [B,N,D+C] from the upstream gradients of x_out [B,N,P] and s_out [B,N,C] (either
+ * may be NULL = zero).  The gradients with respect to x_bin and s_bin are the upstream
+ * gradients themselves and need no kernel. */
+int npa_step_update_backward(const npa_grid *g, const float *y, const float *mask, int32_t channels,
+                             float alpha, float dt, const float *g_x_out, const float *g_s_out, float *g_y,
+                             void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,10 +9,11 @@ reference checkout, or call :func:`npa_b200.install_as_sphops`, and
 from .sph import (HashGrid, HashGridSnapshot, bin_particles, unbin_particles, count, density, blur,
                   gradient, density_gradient, moment_matrix, gradient_hybrid, safe_inv_sym_mat, perceive,
                   enable_fusion, fusion_enabled, set_pair_cache, DensityPair, BlurGradient, perceive_features, PerceiveFeatures,
+                  step_update, StepUpdate,
                   Permute, Count, Density, Blur, Gradient, DensityGradient, MomentMatrix, Perception)
 
 __all__ = [
     "HashGrid", "HashGridSnapshot", "bin_particles", "unbin_particles", "count", "density", "blur",
     "gradient", "density_gradient", "moment_matrix", "gradient_hybrid", "safe_inv_sym_mat", "perceive",
-    "enable_fusion", "fusion_enabled", "set_pair_cache", "perceive_features",
+    "enable_fusion", "fusion_enabled", "set_pair_cache", "perceive_features", "step_update",
 ]

@@ -622,3 +622,47 @@ def perceive_features(x_bin, s_bin, snapshot, eps0, mass=None, log_norm_grad=Tru
         return torch.cat([s_bin, s_blur, g.reshape(B, N, -1), dg], dim=-1)
     return PerceiveFeatures.apply(x_bin, s_bin, mass, snapshot, coef, dg_scale, float(inv_rtol),
                                   bool(log_norm_grad), bool(log_norm_density_grad))
+
+
+class StepUpdate(torch.autograd.Function):
+    """The Euler update of step_euler (models/npa.py:183-203) with the displacement limiter of
+    NPA.forward (models/npa.py:145-153) as one elementwise kernel and one autograd node."""
+
+    @staticmethod
+    def forward(ctx, y, x_bin, s_bin, mask, snapshot, alpha, dt, wrap):
+        x_out, s_out = torch.empty_like(x_bin), torch.empty_like(s_bin)
+        snapshot.grid.step_update_forward(y, x_bin, s_bin, mask, alpha, dt, wrap, x_out, s_out)
+        ctx.save_for_backward(y, *([] if mask is None else [mask]))
+        ctx.has_mask = mask is not None
+        ctx.snapshot = snapshot
+        ctx.consts = (s_bin.shape[2], alpha, dt)
+        ctx.needs = (y.requires_grad, x_bin.requires_grad, s_bin.requires_grad)
+        return x_out, s_out
+
+    @staticmethod
+    def backward(ctx, g_x, g_s):
+        y = ctx.saved_tensors[0]
+        mask = ctx.saved_tensors[1] if ctx.has_mask else None
+        need_y, need_x, need_s = ctx.needs
+        C, alpha, dt = ctx.consts
+        g_x = g_x.contiguous() if g_x is not None else None
+        g_s = g_s.contiguous() if g_s is not None else None
+        g_y = None
+        if need_y:
+            g_y = torch.empty_like(y)
+            ctx.snapshot.grid.step_update_backward(y, mask, C, alpha, dt, g_x, g_s, g_y)
+        return g_y, (g_x if need_x else None), (g_s if need_s else None), None, None, None, None, None
+
+
+def step_update(y, x_bin, s_bin, snapshot, alpha, dt=1.0, update_mask=None, wrap=False):
+    """``(x, s)`` after one Euler step, from the MLP output ``y [B, N, dim + C]`` in cell order.
+
+    ``dx = alpha * y[..., :dim] * eps / (1 + |y[..., :dim]|)``, ``x = x_bin + dt * dx * mask`` (the 3D
+    padding column is carried over), ``s = s_bin + dt * y[..., dim:] * mask``; ``update_mask`` is the
+    reference's ``(rand(B, N, 1) < update_prob).float()`` (or None); ``wrap=True`` also applies
+    ``HashGrid.wrap_positions`` on a periodic grid (keeping the padding column).
+    """
+    if update_mask is not None:
+        update_mask = update_mask.reshape(y.shape[0], y.shape[1]).to(torch.float32).contiguous()
+    return StepUpdate.apply(y.contiguous(), x_bin.contiguous(), s_bin.contiguous(), update_mask, snapshot,
+                            float(alpha), float(dt), bool(wrap))

@@ -430,6 +430,35 @@ class _HashGridBase:
                    N.ptr(g_blur_scratch), N.ptr(g_grad_scratch), N.ptr(g_rho_grad_scratch), N.ptr(grad_rho_scratch),
                    N.ptr(grad_x), N.ptr(grad_s), N.ptr(bin_offsets), N.ptr(block_info), *self._pairs(pair_cache))
 
+    # ---- Euler update after the MLP (no counterpart in the reference module) ----
+    def step_update_forward(self, y, binned_positions, state_in, mask, alpha, dt, wrap, positions_out, state_out):
+        """``x_out = x_bin + dt * limiter(y[..., :D]) * mask``, ``s_out = s_bin + dt * y[..., D:] * mask``
+        (models/npa.py:145-153, 183-203); ``mask`` [B,N] of 0/1 or None."""
+        C = state_in.shape[2] if isinstance(state_in, torch.Tensor) and state_in.dim() == 3 else -1
+        self._pos(binned_positions, "binned_positions")
+        self._pos(positions_out, "positions_out")
+        self._bn(state_in, "state_in", C)
+        self._bn(state_out, "state_out", C)
+        self._bn(y, "y", self._dim + C)
+        if mask is not None:
+            self._bn(mask, "mask")
+        self._call(_lib.npa_step_update_forward, y, self._ref(), N.ptr(y), N.ptr(binned_positions), N.ptr(state_in),
+                   N.ptr(mask), C, float(alpha), float(dt), 1 if wrap else 0, N.ptr(positions_out), N.ptr(state_out))
+
+    def step_update_backward(self, y, mask, channels, alpha, dt, g_positions_out, g_state_out, g_y):
+        """``dL/dy`` of ``step_update_forward``; either upstream gradient may be None (= zero)."""
+        C = int(channels)
+        self._bn(y, "y", self._dim + C)
+        self._bn(g_y, "g_y", self._dim + C)
+        if mask is not None:
+            self._bn(mask, "mask")
+        if g_positions_out is not None:
+            self._pos(g_positions_out, "g_positions_out")
+        if g_state_out is not None:
+            self._bn(g_state_out, "g_state_out", C)
+        self._call(_lib.npa_step_update_backward, y, self._ref(), N.ptr(y), N.ptr(mask), C, float(alpha), float(dt),
+                   N.ptr(g_positions_out), N.ptr(g_state_out), N.ptr(g_y))
+
     # ---- fused perception (no counterpart in the reference module) -------------
     def perception_forward(self, binned_positions, mass, state_in, rho, count, density_gradient_out,
                            state_out, state_gradient_out, moment_matrix_out, bin_offsets, block_info, pair_cache=None):

@@ -18,7 +18,8 @@ def pytest_configure(config):
 
 
 def golden_names():
-    return sorted(p.stem for p in GOLDEN_DIR.glob("*.npz"))
+    """Operator fixtures (tests/golden/make_golden.py); the step_* files belong to make_step_golden.py."""
+    return sorted(p.stem for p in GOLDEN_DIR.glob("*.npz") if not p.stem.startswith("step_"))
 
 
 def load_golden(name):

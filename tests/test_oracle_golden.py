@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import oracle
-from conftest import assert_close, golden_names, load_golden
+from conftest import GOLDEN_DIR, assert_close, golden_names, load_golden
 
 FWD = ["rho", "rho_grad", "blur", "grad", "moment"]
 
@@ -75,3 +75,23 @@ def test_safe_inverse_identity_fallback():
         inv = oracle.safe_inv_sym_mat(m, 1e-3)
         np.testing.assert_array_equal(inv[0], np.eye(dim, dtype=np.float32))
         np.testing.assert_allclose(inv[1:] @ m[1:], np.broadcast_to(np.eye(dim), (49, dim, dim)), atol=2e-4)
+
+
+STEP_CASES = ["step_d2", "step_d3", "step_d2_all"]
+
+
+@pytest.mark.parametrize("name", STEP_CASES)
+def test_step_oracle_matches_reference_step_euler(name):
+    """oracle/step.py against NPA.forward + step_euler of the reference (fixtures made by
+    tests/golden/make_step_golden.py): new positions / states bit for bit, dL/dy to 1e-6."""
+    from oracle import step as step_oracle
+    g = np.load(GOLDEN_DIR / f"{name}.npz")
+    dim, eps, alpha, dt = int(g["dim"]), float(g["eps"]), float(g["alpha"]), float(g["dt"])
+    x, s = step_oracle.step_forward(g["y"], g["x_bin"], g["s_bin"], g["mask"], dim, eps, alpha, dt)
+    np.testing.assert_array_equal(s, g["s_new"])
+    np.testing.assert_allclose(x, g["x_new"], rtol=0, atol=2e-7 * np.abs(g["x_new"]).max())
+    g_y = step_oracle.step_backward(g["y"], g["mask"], dim, eps, alpha, dt, g["up_x"], g["up_s"])
+    np.testing.assert_allclose(g_y, g["g_y"], rtol=1e-5, atol=1e-6 * np.abs(g["g_y"]).max())
+    # gradients with respect to the binned inputs are the upstream gradients themselves
+    np.testing.assert_array_equal(g["g_x_bin"], g["up_x"])
+    np.testing.assert_array_equal(g["g_s_bin"], g["up_s"])
