@@ -122,8 +122,111 @@ __global__ void __launch_bounds__(256) step_update_kernel(StepArgs a, Geom g) {
     }
 }
 
+// Tiled variant for feature counts that are a multiple of 4: a CTA stages the y rows of 64
+// particles in shared memory with 16-byte loads (rows of D + C floats are not 16-byte aligned, the
+// tile as a whole is), so that the state columns move as float4 and the position as one vector per
+// particle.  Backward assembles the dL/dy tile in shared memory the same way.
+constexpr int kStepRows = 64;
+
+template <int D, bool BACKWARD>
+__global__ void __launch_bounds__(256) step_update_tiled_kernel(StepArgs a, Geom g) {
+    extern __shared__ __align__(16) float tile[];  // [kStepRows][D + C]
+    const int W = D + a.C, C4 = a.C / 4;
+    const long long tiles = (a.particles + kStepRows - 1) / kStepRows;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const long long r0 = t * kStepRows;
+        const int rows = (int)(a.particles - r0 < kStepRows ? a.particles - r0 : kStepRows);
+        const int n = rows * W;
+        if (!BACKWARD) {
+            const float *src = a.y + r0 * W;
+            if (n % 4 == 0) {
+                for (int q = threadIdx.x; q < n / 4; q += blockDim.x)
+                    reinterpret_cast<float4 *>(tile)[q] = __ldg(reinterpret_cast<const float4 *>(src) + q);
+            } else {
+                for (int e = threadIdx.x; e < n; e += blockDim.x) tile[e] = __ldg(src + e);
+            }
+            __syncthreads();
+            for (int f = threadIdx.x; f < rows * C4; f += blockDim.x) {
+                const int row = f / C4, c4 = f - row * C4;
+                const long long i = r0 + row;
+                const float m = a.mask ? __ldg(a.mask + i) : 1.0f;
+                const float4 sv = __ldg(reinterpret_cast<const float4 *>(a.s_bin) + i * C4 + c4);
+                const float *yr = tile + row * W + D + 4 * c4;
+                reinterpret_cast<float4 *>(a.s_out)[i * C4 + c4] =
+                    make_float4(sv.x + (a.dt * yr[0]) * m, sv.y + (a.dt * yr[1]) * m, sv.z + (a.dt * yr[2]) * m,
+                                sv.w + (a.dt * yr[3]) * m);
+            }
+            for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+                const long long i = r0 + row;
+                const float m = a.mask ? __ldg(a.mask + i) : 1.0f;
+                const float *yr = tile + row * W;
+                float n2 = 0.f;
+#pragma unroll
+                for (int d = 0; d < D; ++d) n2 = fmaf(yr[d], yr[d], n2);
+                const float den = 1.0f + sqrtf(n2);
+                float xi[4] = {0.f, 0.f, 0.f, 0.f};
+                if (D == 2) {
+                    const float2 v = __ldg(reinterpret_cast<const float2 *>(a.x_bin) + i);
+                    xi[0] = v.x; xi[1] = v.y;
+                } else {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x_bin) + i);
+                    xi[0] = v.x; xi[1] = v.y; xi[2] = v.z; xi[3] = v.w;
+                }
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float lim = ((a.alpha * yr[d]) * a.eps) / den;
+                    xi[d] = xi[d] + (a.dt * lim) * m;
+                    if (a.wrap && g.periodic) xi[d] = wrap_axis(xi[d], g.L[d]);
+                }
+                if (D == 2) reinterpret_cast<float2 *>(a.x_out)[i] = make_float2(xi[0], xi[1]);
+                else reinterpret_cast<float4 *>(a.x_out)[i] = make_float4(xi[0], xi[1], xi[2], xi[3]);
+            }
+            __syncthreads();
+        } else {
+            for (int f = threadIdx.x; f < rows * C4; f += blockDim.x) {
+                const int row = f / C4, c4 = f - row * C4;
+                const long long i = r0 + row;
+                const float k = a.dt * (a.mask ? __ldg(a.mask + i) : 1.0f);
+                float4 gs = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (a.g_s_out) gs = __ldg(reinterpret_cast<const float4 *>(a.g_s_out) + i * C4 + c4);
+                float *o = tile + row * W + D + 4 * c4;
+                o[0] = k * gs.x; o[1] = k * gs.y; o[2] = k * gs.z; o[3] = k * gs.w;
+            }
+            for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+                const long long i = r0 + row;
+#pragma unroll
+                for (int d = 0; d < D; ++d) tile[row * W + d] = step_backward_element<D>(a, i, d);
+            }
+            __syncthreads();
+            float *dst = a.g_y + r0 * W;
+            if (n % 4 == 0) {
+                for (int q = threadIdx.x; q < n / 4; q += blockDim.x)
+                    reinterpret_cast<float4 *>(dst)[q] = reinterpret_cast<const float4 *>(tile)[q];
+            } else {
+                for (int e = threadIdx.x; e < n; e += blockDim.x) dst[e] = tile[e];
+            }
+            __syncthreads();
+        }
+    }
+}
+
+static bool aligned16(const void *p) { return ((uintptr_t)p % 16) == 0; }
+
 template <bool BACKWARD>
 static int launch_step(const Geom &g, const StepArgs &a, cudaStream_t st) {
+    const size_t tile_bytes = (size_t)kStepRows * (g.dim + a.C) * sizeof(float);
+    const bool vec = a.C % 4 == 0 && tile_bytes <= 48 * 1024 &&
+                     (BACKWARD ? aligned16(a.g_y) && aligned16(a.g_s_out) && aligned16(a.g_x_out)
+                               : aligned16(a.y) && aligned16(a.s_bin) && aligned16(a.s_out) && aligned16(a.x_bin) &&
+                                     aligned16(a.x_out));
+    if (vec) {
+        const long long tiles = (a.particles + kStepRows - 1) / kStepRows;
+        const long long cap = 148ll * 8;
+        const int ctas = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+        if (g.dim == 2) step_update_tiled_kernel<2, BACKWARD><<<ctas, 256, tile_bytes, st>>>(a, g);
+        else step_update_tiled_kernel<3, BACKWARD><<<ctas, 256, tile_bytes, st>>>(a, g);
+        return check_launch(BACKWARD ? "step_update_tiled_kernel (backward)" : "step_update_tiled_kernel (forward)");
+    }
     const long long total = a.particles * (g.dim + a.C);
     const long long quads = (total + 3) / 4;
     const long long want = (quads + 255) / 256;
