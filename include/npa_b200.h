@@ -380,6 +380,27 @@ int npa_step_update_backward(const npa_grid *g, const float *y, const float *mas
                              float alpha, float dt, const float *g_x_out, const float *g_s_out, float *g_y,
                              void *stream);
 
+/* ---- 2D Gaussian splatting of particles into an image --------------------------- *
+ * Replaces splat_particles / splat_particles_batch (utils/splatting.py:6-113), the
+ * renderer of the reference's splat loss (losses/splat_loss.py:71-86).
+ *   x [B,N,2] world positions, color [B,N,3]; out [B,img,img,4] = (r, g, b, density).
+ *   pixel position p = (x - lo) / (hi - lo) * (img - 1), y flipped when y_up != 0;
+ *   a particle adds w(dx,dy) = exp(-((dx - frac_x)^2 + (dy - frac_y)^2) / (2 sigma^2)) to the
+ *   pixels floor(p) + (dx,dy), |dx|,|dy| <= radius, that lie inside the image; with
+ *   normalize != 0, w is divided by (1e-8 + its sum over the whole patch) and multiplied by
+ *   norm_scale.  sigma_pixels, radius and norm_scale are the values the reference derives
+ *   from (sigma, img_size, pixel_size, lo, hi) at utils/splatting.py:43-46,75-77.
+ * Every pixel of out is written; sums run in particle order (deterministic). */
+int npa_splat_forward(const float *x, const float *color, int32_t batch, int32_t particles, int32_t img_size,
+                      double sigma_pixels, int32_t radius, double lo, double hi, int32_t y_up,
+                      int32_t normalize, double norm_scale, float *out, void *stream);
+
+/* Gradients of npa_splat_forward: g_x [B,N,2] and g_color [B,N,3] (either may be NULL)
+ * from g_out [B,img,img,4]. */
+int npa_splat_backward(const float *x, const float *color, const float *g_out, int32_t batch, int32_t particles,
+                       int32_t img_size, double sigma_pixels, int32_t radius, double lo, double hi, int32_t y_up,
+                       int32_t normalize, double norm_scale, float *g_x, float *g_color, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,8 +18,9 @@ def pytest_configure(config):
 
 
 def golden_names():
-    """Operator fixtures (tests/golden/make_golden.py); the step_* files belong to make_step_golden.py."""
-    return sorted(p.stem for p in GOLDEN_DIR.glob("*.npz") if not p.stem.startswith("step_"))
+    """Operator fixtures (tests/golden/make_golden.py); the step_* and splat_* files belong to
+    make_step_golden.py and make_splat_golden.py."""
+    return sorted(p.stem for p in GOLDEN_DIR.glob("*.npz") if not p.stem.startswith(("step_", "splat_")))
 
 
 def load_golden(name):

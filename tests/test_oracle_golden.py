@@ -95,3 +95,26 @@ def test_step_oracle_matches_reference_step_euler(name):
     # gradients with respect to the binned inputs are the upstream gradients themselves
     np.testing.assert_array_equal(g["g_x_bin"], g["up_x"])
     np.testing.assert_array_equal(g["g_s_bin"], g["up_s"])
+
+
+SPLAT_CASES = ["splat_default_small", "splat_plain_yup", "splat_wide_box"]
+
+
+@pytest.mark.parametrize("name", SPLAT_CASES)
+def test_splat_oracle_matches_reference_splatting(name):
+    """oracle/splat.py against the reference's splat_particles_batch run in float64 (fixtures made by
+    tests/golden/make_splat_golden.py): image and both gradients to 1e-9."""
+    import ast
+    from oracle import splat as splat_oracle
+    g = np.load(GOLDEN_DIR / f"{name}.npz")
+    meta = ast.literal_eval(str(g["meta"]))
+    for b in range(meta["B"]):
+        x, c = g["x"][b].astype(np.float64), g["color"][b].astype(np.float64)
+        out = splat_oracle.splat_forward(x, c, **meta["kw"])
+        scale = np.abs(g["out_f64"][b]).max()
+        np.testing.assert_allclose(out, g["out_f64"][b], rtol=1e-9, atol=1e-12 * scale)
+        g_x, g_c = splat_oracle.splat_backward(x, c, g["up"][b], **meta["kw"])
+        np.testing.assert_allclose(g_x, g["g_x_f64"][b], rtol=1e-8, atol=1e-10 * np.abs(g["g_x_f64"][b]).max())
+        want_c = g["g_color_f64"][b]
+        np.testing.assert_allclose(g_c, want_c[:, -3:], rtol=1e-9, atol=1e-12 * np.abs(want_c).max())
+        assert not want_c[:, :-3].any()   # only the last three colour channels are rendered
