@@ -390,10 +390,11 @@ int npa_step_update_backward(const npa_grid *g, const float *y, const float *mas
  *   normalize != 0, w is divided by (1e-8 + its sum over the whole patch) and multiplied by
  *   norm_scale.  sigma_pixels, radius and norm_scale are the values the reference derives
  *   from (sigma, img_size, pixel_size, lo, hi) at utils/splatting.py:43-46,75-77.
+ * scale_scratch [B*N] floats (contents undefined) is needed when normalize != 0.
  * Every pixel of out is written; sums run in particle order (deterministic). */
 int npa_splat_forward(const float *x, const float *color, int32_t batch, int32_t particles, int32_t img_size,
                       double sigma_pixels, int32_t radius, double lo, double hi, int32_t y_up,
-                      int32_t normalize, double norm_scale, float *out, void *stream);
+                      int32_t normalize, double norm_scale, float *scale_scratch, float *out, void *stream);
 
 /* Gradients of npa_splat_forward: g_x [B,N,2] and g_color [B,N,3] (either may be NULL)
  * from g_out [B,img,img,4]. */

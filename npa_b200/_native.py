@@ -77,7 +77,7 @@ SIGNATURES = {
     "npa_perception_backward": (ctypes.c_int, [_P, _I32] + [_P] * 13 + [_P, _I32, _P]),
     "npa_step_update_forward": (ctypes.c_int, [_P] * 5 + [_I32, ctypes.c_float, ctypes.c_float, _I32, _P, _P, _P]),
     "npa_splat_forward": (ctypes.c_int, [_P, _P, _I32, _I32, _I32, ctypes.c_double, _I32, ctypes.c_double,
-                                         ctypes.c_double, _I32, _I32, ctypes.c_double, _P, _P]),
+                                         ctypes.c_double, _I32, _I32, ctypes.c_double, _P, _P, _P]),
     "npa_splat_backward": (ctypes.c_int, [_P, _P, _P, _I32, _I32, _I32, ctypes.c_double, _I32, ctypes.c_double,
                                           ctypes.c_double, _I32, _I32, ctypes.c_double, _P, _P, _P]),
     "npa_step_update_backward": (ctypes.c_int, [_P] * 3 + [_I32, ctypes.c_float, ctypes.c_float, _P, _P, _P, _P]),

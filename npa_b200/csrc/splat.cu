@@ -27,6 +27,7 @@ struct SplatArgs {
     const float *g_out;  // backward: upstream of out
     float *g_x;          // backward: [B, N, 2]
     float *g_color;      // backward: [B, N, 3]
+    float *wscale;       // [B, N] scratch: norm_scale / (1e-8 + patch sum) per particle (normalised mode)
     int B, N, img, radius, y_up, normalize;
     float lo, span, sigma, norm_scale;  // span = hi - lo; sigma in pixels
 };
@@ -64,6 +65,19 @@ __device__ inline void axis_sums(int r, float f, float inv2s2, float &s0, float 
     }
 }
 
+// Normalised mode: the scale of every particle, once (the forward tiles would otherwise redo the
+// 2 (2r+1) exponentials for every tile a particle touches).
+__global__ void __launch_bounds__(256) splat_scale_kernel(SplatArgs a) {
+    const long long n = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (n >= (long long)a.B * a.N) return;
+    const SplatPoint p = splat_point(a, n);
+    const float inv2s2 = 1.0f / (2.0f * a.sigma * a.sigma);
+    float sx, sy, unused;
+    axis_sums(a.radius, p.fx, inv2s2, sx, unused);
+    axis_sums(a.radius, p.fy, inv2s2, sy, unused);
+    a.wscale[n] = a.norm_scale / (1e-8f + sx * sy);
+}
+
 __global__ void __launch_bounds__(kSplatTile *kSplatTile) splat_forward_kernel(SplatArgs a) {
     constexpr int T = kSplatTile * kSplatTile;
     __shared__ int s_cx[T], s_cy[T];
@@ -98,13 +112,7 @@ __global__ void __launch_bounds__(kSplatTile *kSplatTile) splat_forward_kernel(S
         }
         if (hit) {
             const int slot = base + __popc(bal & ((1u << lane) - 1u));
-            float scale = 1.0f;
-            if (a.normalize) {
-                float sx, sy, unused;
-                axis_sums(r, p.fx, inv2s2, sx, unused);
-                axis_sums(r, p.fy, inv2s2, sy, unused);
-                scale = a.norm_scale / (1e-8f + sx * sy);
-            }
+            const float scale = a.normalize ? __ldg(a.wscale + (long long)b * a.N + n) : 1.0f;
             const float *c = a.color + ((long long)b * a.N + n) * 3;
             s_cx[slot] = p.cx; s_cy[slot] = p.cy; s_fx[slot] = p.fx; s_fy[slot] = p.fy; s_w[slot] = scale;
             s_r[slot] = __ldg(c); s_g[slot] = __ldg(c + 1); s_b[slot] = __ldg(c + 2);
@@ -168,12 +176,19 @@ __global__ void __launch_bounds__(256) splat_backward_kernel(SplatArgs a) {
     }
     gr = warp_sum(gr); gg = warp_sum(gg); gb = warp_sum(gb);
     a0 = warp_sum(a0); ax = warp_sum(ax); ay = warp_sum(ay);
+    float sx = 0.f, sy = 0.f, t_x = 0.f, t_y = 0.f;
+    if (a.normalize) {  // the axis sums, spread over the lanes
+        for (int d = -r + lane; d <= r; d += 32) {
+            const float ux = (float)d - p.fx, uy = (float)d - p.fy;
+            const float ex = expf(-(ux * ux) * inv2s2), ey = expf(-(uy * uy) * inv2s2);
+            sx += ex; sy += ey;
+            t_x = fmaf(ex, ux, t_x); t_y = fmaf(ey, uy, t_y);
+        }
+        sx = warp_sum(sx); sy = warp_sum(sy); t_x = warp_sum(t_x); t_y = warp_sum(t_y);
+    }
     if (lane != 0) return;
     float scale = 1.0f, gfx = ax, gfy = ay;
     if (a.normalize) {
-        float sx, sy, t_x, t_y;
-        axis_sums(r, p.fx, inv2s2, sx, t_x);
-        axis_sums(r, p.fy, inv2s2, sy, t_y);
         const float inv = 1.0f / (1e-8f + sx * sy);
         scale = a.norm_scale * inv;
         gfx = ax - a0 * inv * (t_x * sy);
@@ -210,16 +225,23 @@ extern "C" {
 
 int npa_splat_forward(const float *x, const float *color, int32_t batch, int32_t particles, int32_t img_size,
                       double sigma_pixels, int32_t radius, double lo, double hi, int32_t y_up, int32_t normalize,
-                      double norm_scale, float *out, void *stream) {
+                      double norm_scale, float *scale_scratch, float *out, void *stream) {
     SplatArgs a = {};
-    a.x = x; a.color = color; a.out = out; a.B = batch; a.N = particles; a.img = img_size; a.radius = radius;
+    a.x = x; a.color = color; a.out = out; a.wscale = scale_scratch; a.B = batch; a.N = particles; a.img = img_size; a.radius = radius;
     a.y_up = y_up; a.normalize = normalize; a.lo = (float)lo; a.span = (float)(hi - lo); a.sigma = (float)sigma_pixels;
     a.norm_scale = (float)norm_scale;
     int rc = check_splat("npa_splat_forward", a);
     if (rc != NPA_OK) return rc;
     if (!out || (uintptr_t)out % 16) return fail(NPA_ERR_INVALID_ARGUMENT, "npa_splat_forward: out must be non-NULL and 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (normalize) {
+        if (!scale_scratch) return fail(NPA_ERR_INVALID_ARGUMENT, "npa_splat_forward: scale_scratch [B*N] is needed when normalize != 0");
+        const long long n = (long long)batch * particles;
+        splat_scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a);
+        if ((rc = check_launch("splat_scale_kernel")) != NPA_OK) return rc;
+    }
     const int tiles = (img_size + kSplatTile - 1) / kSplatTile;
-    splat_forward_kernel<<<dim3(tiles * tiles, batch), kSplatTile * kSplatTile, 0, (cudaStream_t)stream>>>(a);
+    splat_forward_kernel<<<dim3(tiles * tiles, batch), kSplatTile * kSplatTile, 0, st>>>(a);
     return check_launch("splat_forward_kernel");
 }
 

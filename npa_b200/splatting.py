@@ -32,9 +32,10 @@ class _Splat(torch.autograd.Function):
     def forward(ctx, x, color, img_size, sigma_pix, radius, lo, hi, y_up, normalize, scale):
         B, n = x.shape[0], x.shape[1]
         out = torch.empty(B, img_size, img_size, 4, dtype=torch.float32, device=x.device)
+        scratch = torch.empty(B, n, dtype=torch.float32, device=x.device) if normalize else None
         with torch.cuda.device(x.device):
             N.check(_lib.npa_splat_forward(N.ptr(x), N.ptr(color), B, n, img_size, sigma_pix, radius, lo, hi,
-                                           1 if y_up else 0, 1 if normalize else 0, scale, N.ptr(out),
+                                           1 if y_up else 0, 1 if normalize else 0, scale, N.ptr(scratch), N.ptr(out),
                                            N.current_stream()))
         ctx.save_for_backward(x, color)
         ctx.consts = (img_size, sigma_pix, radius, lo, hi, y_up, normalize, scale)
