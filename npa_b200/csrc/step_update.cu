@@ -128,24 +128,42 @@ __global__ void __launch_bounds__(256) step_update_kernel(StepArgs a, Geom g) {
 // particle.  Backward assembles the dL/dy tile in shared memory the same way.
 constexpr int kStepRows = 64;
 
+__device__ inline void tile_copy_async(float *smem_dst, const float *gmem_src, int floats) {
+    // 16-byte pieces; the caller guarantees floats % 4 == 0 and 16-byte aligned addresses
+    for (int q = threadIdx.x; q < floats / 4; q += blockDim.x) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst + 4 * q);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src + 4 * q) : "memory");
+    }
+}
+
 template <int D, bool BACKWARD>
 __global__ void __launch_bounds__(256) step_update_tiled_kernel(StepArgs a, Geom g) {
-    extern __shared__ __align__(16) float tile[];  // [kStepRows][D + C]
+    extern __shared__ __align__(16) float tile_mem[];  // forward: two tiles [kStepRows][D + C]; backward: one
     const int W = D + a.C, C4 = a.C / 4;
     const long long tiles = (a.particles + kStepRows - 1) / kStepRows;
-    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const long long r0 = t * kStepRows;
-        const int rows = (int)(a.particles - r0 < kStepRows ? a.particles - r0 : kStepRows);
-        const int n = rows * W;
-        if (!BACKWARD) {
-            const float *src = a.y + r0 * W;
-            if (n % 4 == 0) {
-                for (int q = threadIdx.x; q < n / 4; q += blockDim.x)
-                    reinterpret_cast<float4 *>(tile)[q] = __ldg(reinterpret_cast<const float4 *>(src) + q);
-            } else {
-                for (int e = threadIdx.x; e < n; e += blockDim.x) tile[e] = __ldg(src + e);
-            }
-            __syncthreads();
+    auto rows_of = [&](long long t) {
+        const long long left = a.particles - t * kStepRows;
+        return (int)(left < kStepRows ? left : kStepRows);
+    };
+    if (!BACKWARD) {
+        // The y tile of the next iteration is copied (cp.async) while the current one is processed.
+        // A tile whose float count is not a multiple of 4 (only the last one can be) is loaded directly.
+        long long t = blockIdx.x;
+        int buf = 0;
+        if (t < tiles && (rows_of(t) * W) % 4 == 0) tile_copy_async(tile_mem, a.y + t * kStepRows * W, rows_of(t) * W);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        for (; t < tiles; t += gridDim.x, buf ^= 1) {
+            float *tile = tile_mem + (size_t)buf * kStepRows * W;
+            const long long r0 = t * kStepRows;
+            const int rows = rows_of(t), n = rows * W;
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            if (n % 4 != 0)
+                for (int e = threadIdx.x; e < n; e += blockDim.x) tile[e] = __ldg(a.y + r0 * W + e);
+            __syncthreads();  // tile t is complete, and every thread has finished with the other buffer
+            const long long tn = t + gridDim.x;
+            if (tn < tiles && (rows_of(tn) * W) % 4 == 0)
+                tile_copy_async(tile_mem + (size_t)(buf ^ 1) * kStepRows * W, a.y + tn * kStepRows * W, rows_of(tn) * W);
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
             for (int f = threadIdx.x; f < rows * C4; f += blockDim.x) {
                 const int row = f / C4, c4 = f - row * C4;
                 const long long i = r0 + row;
@@ -181,8 +199,16 @@ __global__ void __launch_bounds__(256) step_update_tiled_kernel(StepArgs a, Geom
                 if (D == 2) reinterpret_cast<float2 *>(a.x_out)[i] = make_float2(xi[0], xi[1]);
                 else reinterpret_cast<float4 *>(a.x_out)[i] = make_float4(xi[0], xi[1], xi[2], xi[3]);
             }
-            __syncthreads();
-        } else {
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        return;
+    }
+    float *tile = tile_mem;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const long long r0 = t * kStepRows;
+        const int rows = rows_of(t);
+        const int n = rows * W;
+        {
             for (int f = threadIdx.x; f < rows * C4; f += blockDim.x) {
                 const int row = f / C4, c4 = f - row * C4;
                 const long long i = r0 + row;
@@ -214,7 +240,8 @@ static bool aligned16(const void *p) { return ((uintptr_t)p % 16) == 0; }
 
 template <bool BACKWARD>
 static int launch_step(const Geom &g, const StepArgs &a, cudaStream_t st) {
-    const size_t tile_bytes = (size_t)kStepRows * (g.dim + a.C) * sizeof(float);
+    // forward keeps two tiles (the next one is copied while the current one is processed)
+    const size_t tile_bytes = (size_t)(BACKWARD ? 1 : 2) * kStepRows * (g.dim + a.C) * sizeof(float);
     const bool vec = a.C % 4 == 0 && tile_bytes <= 48 * 1024 &&
                      (BACKWARD ? aligned16(a.g_y) && aligned16(a.g_s_out) && aligned16(a.g_x_out)
                                : aligned16(a.y) && aligned16(a.s_bin) && aligned16(a.s_out) && aligned16(a.x_bin) &&
