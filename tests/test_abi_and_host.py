@@ -153,3 +153,38 @@ def test_reference_model_imports_on_top_of_this_package():
                 sys.modules.pop(k, None)
             else:
                 sys.modules[k] = v
+
+
+def test_step_update_and_splat_reject_bad_arguments_before_any_launch():
+    """Validation happens on the host, ahead of the first CUDA call, so it can be checked without a GPU."""
+    from npa_b200 import _native as n
+    g = n.make_grid(2, "clamped", "grid", (16, 16), 0.1, 1, 128, 32)
+    ref = ctypes.byref(g)
+    buf = ctypes.c_void_p(256)  # a non-NULL, 16-byte aligned dummy address; never dereferenced
+    null = ctypes.c_void_p(0)
+    lib = n.lib
+    assert lib.npa_step_update_forward(ref, buf, buf, buf, null, 0, 1.0, 1.0, 0, buf, buf, null) == n.NPA_ERR_INVALID_ARGUMENT
+    assert "channels" in n.last_error()
+    assert lib.npa_step_update_forward(ref, null, buf, buf, null, 8, 1.0, 1.0, 0, buf, buf, null) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lib.npa_step_update_backward(ref, buf, null, 8, 1.0, 1.0, buf, buf, null, null) == n.NPA_ERR_INVALID_ARGUMENT
+    # splat: radius outside the supported range, non-positive sizes, missing scratch in normalised mode
+    args = lambda radius, scratch, N=64: (buf, buf, 1, N, 64, 2.0, radius, -1.0, 1.0, 0, 1, 1.0, scratch, buf, null)
+    assert lib.npa_splat_forward(*args(65, buf)) == n.NPA_ERR_UNSUPPORTED
+    assert "radius" in n.last_error()
+    assert lib.npa_splat_forward(*args(0, buf)) == n.NPA_ERR_UNSUPPORTED
+    assert lib.npa_splat_forward(*args(10, buf, N=0)) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lib.npa_splat_forward(*args(10, null)) == n.NPA_ERR_INVALID_ARGUMENT
+    assert "scale_scratch" in n.last_error()
+    assert lib.npa_splat_backward(buf, buf, null, 1, 64, 64, 2.0, 10, -1.0, 1.0, 0, 1, 1.0, buf, buf, null) == n.NPA_ERR_INVALID_ARGUMENT
+
+
+def test_splat_wrapper_derives_the_reference_constants():
+    """sigma in pixels, patch radius and colour scale as utils/splatting.py:43-46,75-77 derives them."""
+    from npa_b200.splatting import _derived
+    from oracle.splat import derived
+    for kw in (dict(img_size=256, sigma=2.0, lo=-1.0, hi=1.0, normalize_color=True, pixel_size=2.0 / 128.0),
+               dict(img_size=64, sigma=1.5, lo=-2.0, hi=1.5, normalize_color=True, pixel_size=0.05),
+               dict(img_size=32, sigma=0.1, lo=-1.0, hi=1.0, normalize_color=False, pixel_size=1.0)):
+        assert _derived(**kw) == derived(**kw)
+    assert _derived(256, 2.0, -1.0, 1.0, True, 2.0 / 128.0) == (4.0, 20, 4.0)
+    assert _derived(32, 0.1, -1.0, 1.0, False, 1.0) == (0.1, 1, 1.0)
