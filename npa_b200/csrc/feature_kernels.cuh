@@ -34,6 +34,7 @@ constexpr int kBwdStages = 2;       // same, backward (five pieces per pair)
 constexpr int kBwdFullWarps = 4;
 constexpr int kBwdFullCtas = 5;
 constexpr int bwd_warps(bool full) { return full ? kBwdFullWarps : kWarpsPerCta; }
+constexpr bool kFwdRing = false;    // forward: cp.async ring (true) or three register sets (false)
 constexpr bool kBwdRing = true;     // backward: cp.async ring (true) or register double buffer (false)
 
 template <int VW>
@@ -137,7 +138,7 @@ __device__ inline void expand_pairs(const Geom &g, const float *__restrict__ x, 
 }
 
 template <int D, bool PER, int LPP, int VW, int MASK>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, (MASK & (F_MOMENT | F_PACK)) ? 3 : 4)
 feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     constexpr int PP = 32 / LPP;  // pairs drained in parallel
     constexpr int S = kFwdStages;
@@ -225,16 +226,8 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                         }
                         async_commit();
                     };
-#pragma unroll
-                    for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
-                    int slot = 0;
-                    for (int e = sg; e < n; e += PP) {
+                    auto consume = [&](int e, const float (&sj)[VW]) {
                         const float4 en = ent[e];
-                        async_wait<S - 1>();
-                        const Piece<VW> pj = ring[slot * 32];
-                        float sj[VW];
-#pragma unroll
-                        for (int q = 0; q < VW; ++q) sj[q] = pj.v[q];
 #pragma unroll
                         for (int q = 0; q < VW; ++q) {
                             if (MASK & F_BLUR) blur[q] = fmaf(en.w, sj[q], blur[q]);
@@ -245,11 +238,46 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                                 if (D == 3) gr[q * D + 2] = fmaf(df, en.z, gr[q * D + 2]);
                             }
                         }
-                        // refill the slot only after its values were consumed by the arithmetic above
-                        fetch(e + S * PP, slot);
-                        slot = slot + 1 == S ? 0 : slot + 1;
+                    };
+                    if (kFwdRing) {
+#pragma unroll
+                        for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
+                        int slot = 0;
+                        for (int e = sg; e < n; e += PP) {
+                            async_wait<S - 1>();
+                            const Piece<VW> pj = ring[slot * 32];
+                            float sj[VW];
+#pragma unroll
+                            for (int q = 0; q < VW; ++q) sj[q] = pj.v[q];
+                            consume(e, sj);
+                            // refill the slot only after its values were consumed by the arithmetic above
+                            fetch(e + S * PP, slot);
+                            slot = slot + 1 == S ? 0 : slot + 1;
+                        }
+                        async_wait<0>();
+                    } else {
+                        // three register sets, the rows of the next two pairs in flight
+                        auto load = [&](int e, float (&sj)[VW]) {
+                            if (e < n) load_feat<VW>(a.s + ((long long)__float_as_int(geo[e].w) * C + f0), sj);
+                        };
+                        float r0[VW] = {}, r1[VW] = {}, r2[VW] = {};
+                        int e = sg;
+                        load(e, r0);
+                        load(e + PP, r1);
+                        while (e < n) {
+                            load(e + 2 * PP, r2);
+                            consume(e, r0);
+                            e += PP;
+                            if (e >= n) break;
+                            load(e + 2 * PP, r0);
+                            consume(e, r1);
+                            e += PP;
+                            if (e >= n) break;
+                            load(e + 2 * PP, r1);
+                            consume(e, r2);
+                            e += PP;
+                        }
                     }
-                    async_wait<0>();
                 }
                 cached += n;
                 __syncwarp();
@@ -637,7 +665,7 @@ inline bool feature_rows_vectorisable(int C, const void *p0, const void *p1, con
 template <int VW, typename Kernel>
 int launch_feature_forward_mask(const Geom &g, Kernel kernel, const FeatureFwdArgs &a, cudaStream_t st) {
     const int threads = kWarpsPerCta * 32;
-    const size_t dyn = (size_t)kWarpsPerCta * kFwdStages * 32 * sizeof(Piece<VW>);
+    const size_t dyn = kFwdRing ? (size_t)kWarpsPerCta * kFwdStages * 32 * sizeof(Piece<VW>) : 0;
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
