@@ -237,6 +237,9 @@ def run_gpu_arm(args, w):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        from npa_b200.sharding import bind_to_gpu_cpus
+        bound = bind_to_gpu_cpus(local_rank)  # pinned buffers below land on the GPU's NUMA node
+        print(f"[bench] rank {rank}: bound to {len(bound) if bound else 'no'} cores near GPU {local_rank}", file=sys.stderr)
         dist.init_process_group("nccl", device_id=dev)
 
     # every rank owns its own B independent systems (batch sharded over ranks, weak scaling)

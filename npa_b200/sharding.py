@@ -53,6 +53,37 @@ def init_from_env(backend: Optional[str] = None) -> Tuple[int, int, int]:
     return rank, world, local_rank
 
 
+def bind_to_gpu_cpus(device_index: int) -> Optional[set]:
+    """Restrict this process to the CPU cores the driver reports as closest to the GPU (its NUMA
+    node), so that the pinned host buffers allocated afterwards sit on that node and host <-> device
+    copies of the ranks of one machine do not all cross the socket interconnect.  Read-only use of
+    NVML; returns the core set, or None when it cannot be determined (nothing is changed then).
+    ``device_index`` counts visible devices (CUDA_VISIBLE_DEVICES is honoured)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible:
+                ident = visible.split(",")[device_index].strip()
+                handle = (pynvml.nvmlDeviceGetHandleByUUID(ident) if ident.startswith("GPU-")
+                          else pynvml.nvmlDeviceGetHandleByIndex(int(ident)))
+            else:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            words = (os.cpu_count() + 63) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return cpus
+    except Exception:
+        return None
+
+
 def local_grid(rank: int, world: int, *, batch_size: int, **hashgrid_kwargs):
     """``HashGrid`` for this rank's share of a global batch of ``batch_size`` systems."""
     from .sphops import HashGrid

@@ -76,3 +76,12 @@ def test_allreduce_is_a_no_op_without_a_group():
     before = [p.grad.clone() for p in model.parameters()]
     assert allreduce_gradients(model.parameters()) == 0
     assert all(torch.equal(a, p.grad) for a, p in zip(before, model.parameters()))
+
+
+def test_cpu_binding_is_a_no_op_without_nvml():
+    """Without a GPU driver the helper reports None and leaves the affinity of the process alone."""
+    import os
+    from npa_b200.sharding import bind_to_gpu_cpus
+    before = os.sched_getaffinity(0)
+    assert bind_to_gpu_cpus(0) is None
+    assert os.sched_getaffinity(0) == before
