@@ -2,6 +2,7 @@
 
     python -m npa_b200.microbench step_update [--workload cfg4_3d_splat]
     python -m npa_b200.microbench splat [--systems 8 --particles 4096]
+    python -m npa_b200.microbench euler_step [--workload cfg4_3d_splat]
 
 Each prints one JSON line.  CUDA events on torch's current stream; inputs rotate over several
 buffer sets larger than L2 so that consecutive launches do not find their inputs cached.  The
@@ -128,9 +129,61 @@ def bench_splat(args):
             "max_abs_difference_to_torch": diff}
 
 
+class _Model(torch.nn.Module):
+    """An NPA-shaped module (models/npa.py:14-75): the attributes a step reads and the 2-layer MLP."""
+
+    def __init__(self, dim, C, hidden=128, eps0=0.1, alpha=1.0):
+        super().__init__()
+        self.spatial_dims, self.state_dims = dim, C
+        self.eps0, self.alpha = eps0, alpha
+        self.state_grad = self.density_grad = self.log_norm_grad = self.log_norm_density_grad = True
+        self.stopgrad_pos, self.stopgrad_state = True, False
+        self.model = torch.nn.Sequential(torch.nn.Linear(2 * C + C * dim + dim, hidden), torch.nn.ReLU(),
+                                         torch.nn.Linear(hidden, dim + C, bias=False))
+
+
+def bench_euler_step(args):
+    """One training step of an NPA model: step_euler forward (grid build, reorder, packed perception,
+    MLP, fused update) + backward to the MLP weights and the input states, and the share of the MLP
+    (torch / cuBLAS fp32) in it."""
+    from .stepping import step_euler
+    from .workloads import make_inputs
+    w = CONFIGS[args.workload]
+    B, N, C, D = w.B, w.N, w.C, w.dim
+    grid = sph.HashGrid(dim=D, boundary=w.boundary, mode=w.mode, grid_size=w.grid_size, eps=w.eps, num_particles=N,
+                        batch_size=B, max_particles_per_block=w.max_particles_per_block)
+    torch.manual_seed(0)
+    model = _Model(D, C).cuda()
+    x, s, _ = make_inputs(w, seed=0)
+    x, s = x.cuda(), s.cuda()
+    up_x, up_s = torch.randn_like(x), torch.randn_like(s)
+    z = torch.randn(B, N, 2 * C + C * D + D, device="cuda")
+    up_y = torch.randn(B, N, D + C, device="cuda")
+
+    def full(_):
+        model.zero_grad(set_to_none=True)
+        sr = s.clone().requires_grad_(True)
+        x_new, s_new, _ = step_euler(model, x, sr, grid, dt=1.0, update_prob=0.5)
+        torch.autograd.backward([x_new, s_new], [up_x, up_s])
+
+    def mlp_only(_):
+        model.zero_grad(set_to_none=True)
+        zr = z.clone().requires_grad_(True)
+        model.model(zr).backward(up_y)
+
+    def forward_only(_):
+        with torch.no_grad():
+            step_euler(model, x, s, grid, dt=1.0, update_prob=0.5)
+
+    reps = max(5, args.reps)
+    return {"kernel": "euler_step", "workload": w.name, "particles": B * N, "mlp": [2 * C + C * D + D, 128, D + C],
+            "train_step_ms": _time(full, [None], reps), "forward_only_ms": _time(forward_only, [None], reps),
+            "mlp_forward_backward_ms": _time(mlp_only, [None], reps)}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["step_update", "splat"])
+    ap.add_argument("what", choices=["step_update", "splat", "euler_step"])
     ap.add_argument("--workload", default="cfg4_3d_splat")
     ap.add_argument("--systems", type=int, default=8)
     ap.add_argument("--particles", type=int, default=4096)
@@ -138,7 +191,7 @@ def main():
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise RuntimeError("npa_b200.microbench needs a CUDA device: the kernels have no CPU fallback")
-    out = bench_step_update(args) if args.what == "step_update" else bench_splat(args)
+    out = {"step_update": bench_step_update, "splat": bench_splat, "euler_step": bench_euler_step}[args.what](args)
     print(json.dumps(out), flush=True)
 
 
