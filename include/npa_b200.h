@@ -402,6 +402,20 @@ int npa_splat_backward(const float *x, const float *color, const float *g_out, i
                        int32_t img_size, double sigma_pixels, int32_t radius, double lo, double hi, int32_t y_up,
                        int32_t normalize, double norm_scale, float *g_x, float *g_color, void *stream);
 
+/* ---- weight gradients of the per-particle MLP ------------------------------------ *
+ * The adaptation MLP of an NPA model (models/npa.py:63-75) is Linear(in, 128) -> ReLU ->
+ * Linear(128, out, bias = False), applied to every particle.  One pass over the rows gives
+ *   dW1 [128, in] = dh^T z,   dW2 [out, 128] = dy^T h,   db1 [128] = sum over rows of dh
+ * from z [rows, in] (the perception rows), h [rows, 128] (hidden activations after the ReLU),
+ * dh [rows, 128] (gradient at the hidden layer, ReLU mask applied) and dy [rows, out]; these
+ * replace three tall-skinny library kernels of torch's autograd.  hidden must be 128, in <= 176,
+ * out <= 48.  scratch (contents undefined) holds the per-CTA partial sums, which are added in a
+ * fixed order: the results are deterministic.  The outputs are overwritten, not accumulated. */
+int64_t npa_mlp_weight_grad_scratch_floats(int64_t rows, int32_t in_dim, int32_t out_dim);
+int npa_mlp_weight_grad(const float *z, const float *dh, const float *h, const float *dy, int64_t rows,
+                        int32_t in_dim, int32_t hidden, int32_t out_dim, float *scratch, int64_t scratch_floats,
+                        float *dW1, float *dW2, float *db1, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

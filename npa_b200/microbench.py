@@ -171,6 +171,12 @@ def bench_euler_step(args):
         zr = z.clone().requires_grad_(True)
         model.model(zr).backward(up_y)
 
+    def mlp_fused(_):
+        from .mlp import apply_mlp
+        model.zero_grad(set_to_none=True)
+        zr = z.clone().requires_grad_(True)
+        apply_mlp(model.model, zr).backward(up_y)
+
     def forward_only(_):
         with torch.no_grad():
             step_euler(model, x, s, grid, dt=1.0, update_prob=0.5)
@@ -178,7 +184,8 @@ def bench_euler_step(args):
     reps = max(5, args.reps)
     return {"kernel": "euler_step", "workload": w.name, "particles": B * N, "mlp": [2 * C + C * D + D, 128, D + C],
             "train_step_ms": _time(full, [None], reps), "forward_only_ms": _time(forward_only, [None], reps),
-            "mlp_forward_backward_ms": _time(mlp_only, [None], reps)}
+            "mlp_forward_backward_ms": _time(mlp_fused, [None], reps),
+            "torch_mlp_forward_backward_ms": _time(mlp_only, [None], reps)}
 
 
 def main():

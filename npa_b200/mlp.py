@@ -1,0 +1,71 @@
+"""The per-particle adaptation MLP of an NPA model with a fused weight-gradient pass.
+
+The reference's MLP (models/npa.py:63-75) is ``Linear(in, hidden) -> ReLU -> Linear(hidden, out,
+bias=False)`` applied to every particle.  Its two forward GEMMs and the two input-gradient GEMMs
+stay library calls (torch / cuBLAS, fp32); the gradients of the weights -- three reductions over
+all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one kernel
+(``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` with that backward when
+``module`` has the reference's structure and a hidden width of 128, and plain ``module(z)``
+otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+
+_lib = N.lib
+HIDDEN = 128
+MAX_IN, MAX_OUT = 176, 48
+
+
+class _AdaptationMLP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, w1, b1, w2):
+        rows = z.reshape(-1, z.shape[-1])
+        h = torch.addmm(b1, rows, w1.t()).relu_()
+        y = h @ w2.t()
+        ctx.save_for_backward(rows, h, w1, w2)
+        ctx.z_shape = z.shape
+        return y.reshape(*z.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, g_y):
+        rows, h, w1, w2 = ctx.saved_tensors
+        need_z, need_w1, need_b1, need_w2 = ctx.needs_input_grad
+        dy = g_y.reshape(-1, g_y.shape[-1]).contiguous()
+        dh = torch.ops.aten.threshold_backward(dy @ w2, h, 0.0)   # ReLU mask from the saved activations
+        g_z = (dh @ w1).reshape(ctx.z_shape) if need_z else None
+        g_w1 = g_b1 = g_w2 = None
+        if need_w1 or need_b1 or need_w2:
+            m, k, o = rows.shape[0], rows.shape[1], w2.shape[0]
+            g_w1, g_b1, g_w2 = torch.empty_like(w1), torch.empty(HIDDEN, dtype=w1.dtype, device=w1.device), torch.empty_like(w2)
+            n_scratch = _lib.npa_mlp_weight_grad_scratch_floats(m, k, o)
+            scratch = torch.empty(n_scratch, dtype=torch.float32, device=rows.device)
+            with torch.cuda.device(rows.device):
+                N.check(_lib.npa_mlp_weight_grad(N.ptr(rows), N.ptr(dh), N.ptr(h), N.ptr(dy), m, k, HIDDEN, o,
+                                                 N.ptr(scratch), n_scratch, N.ptr(g_w1), N.ptr(g_w2), N.ptr(g_b1),
+                                                 N.current_stream()))
+        return g_z, (g_w1 if need_w1 else None), (g_b1 if need_b1 else None), (g_w2 if need_w2 else None)
+
+
+def supported(module) -> bool:
+    """True for ``Sequential(Linear(in, 128), ReLU, Linear(128, out, bias=False))`` in float32 on a
+    CUDA device with ``in <= 176`` and ``out <= 48`` -- the shape of the reference's adaptation MLP."""
+    if not (isinstance(module, torch.nn.Sequential) and len(module) == 3):
+        return False
+    l1, act, l2 = module[0], module[1], module[2]
+    if not (isinstance(l1, torch.nn.Linear) and isinstance(act, torch.nn.ReLU) and isinstance(l2, torch.nn.Linear)):
+        return False
+    if l1.bias is None or l2.bias is not None or l1.out_features != HIDDEN or l2.in_features != HIDDEN:
+        return False
+    if l1.in_features > MAX_IN or l2.out_features > MAX_OUT:
+        return False
+    return l1.weight.is_cuda and l1.weight.dtype == torch.float32 and l2.weight.dtype == torch.float32
+
+
+def apply_mlp(module, z):
+    """``module(z)``; with the fused weight-gradient backward when ``supported(module)``."""
+    if not (supported(module) and z.is_cuda and z.dtype == torch.float32):
+        return module(z)
+    return _AdaptationMLP.apply(z.contiguous(), module[0].weight, module[0].bias, module[2].weight)

@@ -4,7 +4,8 @@
 works on the reference's ``NPA`` module unchanged (it reads ``model.model``, ``alpha``, ``eps0``,
 ``spatial_dims`` and the perception flags), but runs
 
-    grid build -> reorder -> packed perception (two neighbour sweeps) -> model.model (torch MLP)
+    grid build -> reorder -> packed perception (two neighbour sweeps) -> model.model (torch GEMMs,
+    weight gradients by one fused kernel)
     -> fused limiter + update (+ wrap)
 
 instead of five neighbour sweeps and ~25 elementwise torch kernels.  Values and gradients are
@@ -17,6 +18,7 @@ import math
 import torch
 
 from . import sphops as sph
+from .mlp import apply_mlp
 
 
 def _scalar(v) -> float:
@@ -68,7 +70,7 @@ def step_euler(model, x, s, grid, dt=1.0, update_prob=0.5, intermediate=False, n
     B, N, C = s.shape
     z, x_bin, s_bin, snapshot = perceive(model, x, s, grid)
     model.last_snapshot = snapshot
-    y = model.model(z)  # (B, N, dim + C)
+    y = apply_mlp(model.model, z)  # (B, N, dim + C); torch GEMMs, fused weight-gradient kernel in the backward
 
     stats = None
     if intermediate:

@@ -1,0 +1,63 @@
+"""The adaptation MLP with the fused weight-gradient kernel (npa_mlp_weight_grad, npa_b200.mlp)
+against torch autograd: same forward values, gradients held to float64 truth no worse than torch's
+own float32 backward."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mlp(k, o, hidden=128, seed=0):
+    torch.manual_seed(seed)
+    return torch.nn.Sequential(torch.nn.Linear(k, hidden), torch.nn.ReLU(), torch.nn.Linear(hidden, o, bias=False)).cuda()
+
+
+@pytest.mark.parametrize("rows,k,o", [(1000, 66, 18), (4096 + 7, 163, 35), (31, 176, 48), (2048, 5, 1), (65536 * 4, 163, 35)])
+def test_gradients_match_float64_truth(rows, k, o):
+    from npa_b200.mlp import apply_mlp, supported
+    mlp = _mlp(k, o)
+    assert supported(mlp)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    shape = (2, rows // 2, k) if rows % 2 == 0 else (rows, k)
+    z = torch.randn(*shape, generator=g, device="cuda")
+    up = torch.randn(*shape[:-1], o, generator=g, device="cuda")
+
+    def run(fn, module, dtype):
+        module.zero_grad(set_to_none=True)
+        zr = z.detach().clone().to(dtype).requires_grad_(True)
+        y = fn(module, zr)
+        y.backward(up.to(dtype))
+        return [y.detach(), zr.grad] + [p.grad.clone() for p in module.parameters()]
+
+    ours = run(apply_mlp, mlp, torch.float32)
+    theirs = run(lambda m, t: m(t), mlp, torch.float32)
+    truth = run(lambda m, t: m(t), _mlp(k, o).double(), torch.float64)
+    names = ["y", "g_z", "g_W1", "g_b1", "g_W2"]
+    for name, a, b, t in zip(names, ours, theirs, truth):
+        scale = float(t.abs().max())
+        err_ours = float((a.double() - t).abs().max())
+        err_torch = float((b.double() - t).abs().max())
+        assert err_ours <= 2 * err_torch + 2e-6 * scale, (name, err_ours, err_torch, scale)
+    # the forward and the input gradient are the same library calls: identical bits
+    assert torch.equal(ours[0], theirs[0])
+
+
+def test_two_runs_are_bit_identical_and_unsupported_shapes_fall_back():
+    from npa_b200.mlp import apply_mlp, supported
+    mlp = _mlp(66, 18)
+    z = torch.randn(3, 5000, 66, device="cuda")
+    up = torch.randn(3, 5000, 18, device="cuda")
+    grads = []
+    for _ in range(2):
+        mlp.zero_grad(set_to_none=True)
+        apply_mlp(mlp, z.clone().requires_grad_(True)).backward(up)
+        grads.append([p.grad.clone() for p in mlp.parameters()])
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
+    wide = _mlp(66, 18, hidden=64)
+    assert not supported(wide)
+    zr = z.clone().requires_grad_(True)
+    apply_mlp(wide, zr).backward(up)      # plain module call
+    assert zr.grad is not None and wide[0].weight.grad is not None
+    big = _mlp(200, 18)
+    assert not supported(big)
