@@ -188,3 +188,19 @@ def test_splat_wrapper_derives_the_reference_constants():
         assert _derived(**kw) == derived(**kw)
     assert _derived(256, 2.0, -1.0, 1.0, True, 2.0 / 128.0) == (4.0, 20, 4.0)
     assert _derived(32, 0.1, -1.0, 1.0, False, 1.0) == (0.1, 1, 1.0)
+
+
+def test_mlp_weight_grad_rejects_unsupported_shapes_before_any_launch():
+    from npa_b200 import _native as n
+    buf, null = ctypes.c_void_p(256), ctypes.c_void_p(0)
+    lib = n.lib
+    need = lib.npa_mlp_weight_grad_scratch_floats(262144, 163, 35)
+    assert need == 148 * (128 * 163 + 35 * 128 + 128)
+    assert lib.npa_mlp_weight_grad_scratch_floats(40, 66, 18) == 2 * (128 * 66 + 18 * 128 + 128)  # two slabs of 32 rows
+    call = lambda rows, k, h, o, scratch_floats=1 << 40: lib.npa_mlp_weight_grad(
+        buf, buf, buf, buf, rows, k, h, o, buf, scratch_floats, buf, buf, buf, null)
+    assert call(1000, 66, 64, 18) == n.NPA_ERR_UNSUPPORTED and "hidden" in n.last_error()
+    assert call(1000, 177, 128, 18) == n.NPA_ERR_UNSUPPORTED
+    assert call(1000, 66, 128, 49) == n.NPA_ERR_UNSUPPORTED
+    assert call(0, 66, 128, 18) == n.NPA_ERR_INVALID_ARGUMENT
+    assert call(1000, 66, 128, 18, scratch_floats=10) == n.NPA_ERR_SCRATCH_TOO_SMALL
