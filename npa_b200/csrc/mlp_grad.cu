@@ -38,22 +38,25 @@ __device__ inline void slab_copy_async(float *dst, const float *src, int floats)
 }
 
 // Thread (ti, tj) of a 16 x 16 arrangement owns
-//   dW1[i][j]  for i = 8 ti .. 8 ti + 7 and j = tj + 16 k (k < 11),
-//   dW2[o][i'] for i' = 8 tj .. 8 tj + 7 and o = ti + 16 k (k < 3),
+//   dW1[i][j]  for i = 8 ti .. 8 ti + 7 and j = tj + 16 k (k < NJ, NJ >= ceil(in / 16)),
+//   dW2[o][i'] for i' = 8 tj .. 8 tj + 7 and o = ti + 16 k (k < NO, NO >= ceil(out / 16)),
 //   db1[i]     for its 8 i when tj == 0.
+// Columns j >= in (o >= out) of the last k are read from whatever follows in the tile and never
+// written out: the loads carry no bounds test (the tile is followed by 16 floats of padding).
+template <int NJ, int NO>
 __global__ void __launch_bounds__(kMlpThreads, 1) mlp_weight_grad_kernel(MlpGradArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int K = a.in_dim, O = a.out_dim, H = kMlpHidden;
-    const int slab_floats = kMlpRows * (K + 2 * H + O);
+    const int slab_floats = kMlpRows * (K + 2 * H + O) + 16;  // + padding read by the unguarded loads
     const int ti = threadIdx.x >> 4, tj = threadIdx.x & 15;
-    float acc1[8][11], acc2[3][8], accb[8];
+    float acc1[8][NJ], acc2[NO][8], accb[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         accb[i] = 0.f;
 #pragma unroll
-        for (int k = 0; k < 11; ++k) acc1[i][k] = 0.f;
+        for (int k = 0; k < NJ; ++k) acc1[i][k] = 0.f;
 #pragma unroll
-        for (int k = 0; k < 3; ++k) acc2[k][i] = 0.f;
+        for (int k = 0; k < NO; ++k) acc2[k][i] = 0.f;
     }
     const long long slabs = (a.rows + kMlpRows - 1) / kMlpRows;
     auto rows_of = [&](long long s) {
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_weight_grad_kernel(MlpGrad
         const float *dht = zt + kMlpRows * K, *ht = dht + kMlpRows * H, *dyt = ht + kMlpRows * H;
         const int n = rows_of(s);
         for (int r = 0; r < n; ++r) {
-            float dv[8], hv[8], zv[11], yv[3];
+            float dv[8], hv[8], zv[NJ], yv[NO];
             const float4 d0 = *reinterpret_cast<const float4 *>(dht + r * H + 8 * ti);
             const float4 d1 = *reinterpret_cast<const float4 *>(dht + r * H + 8 * ti + 4);
             dv[0] = d0.x; dv[1] = d0.y; dv[2] = d0.z; dv[3] = d0.w; dv[4] = d1.x; dv[5] = d1.y; dv[6] = d1.z; dv[7] = d1.w;
@@ -100,15 +103,15 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_weight_grad_kernel(MlpGrad
             const float4 h1 = *reinterpret_cast<const float4 *>(ht + r * H + 8 * tj + 4);
             hv[0] = h0.x; hv[1] = h0.y; hv[2] = h0.z; hv[3] = h0.w; hv[4] = h1.x; hv[5] = h1.y; hv[6] = h1.z; hv[7] = h1.w;
 #pragma unroll
-            for (int k = 0; k < 11; ++k) zv[k] = tj + 16 * k < K ? zt[r * K + tj + 16 * k] : 0.f;
+            for (int k = 0; k < NJ; ++k) zv[k] = zt[r * K + tj + 16 * k];
 #pragma unroll
-            for (int k = 0; k < 3; ++k) yv[k] = ti + 16 * k < O ? dyt[r * O + ti + 16 * k] : 0.f;
+            for (int k = 0; k < NO; ++k) yv[k] = dyt[r * O + ti + 16 * k];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
 #pragma unroll
-                for (int k = 0; k < 11; ++k) acc1[i][k] = fmaf(dv[i], zv[k], acc1[i][k]);
+                for (int k = 0; k < NJ; ++k) acc1[i][k] = fmaf(dv[i], zv[k], acc1[i][k]);
 #pragma unroll
-                for (int k = 0; k < 3; ++k) acc2[k][i] = fmaf(yv[k], hv[i], acc2[k][i]);
+                for (int k = 0; k < NO; ++k) acc2[k][i] = fmaf(yv[k], hv[i], acc2[k][i]);
                 accb[i] += dv[i];
             }
         }
@@ -120,10 +123,10 @@ __global__ void __launch_bounds__(kMlpThreads, 1) mlp_weight_grad_kernel(MlpGrad
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
 #pragma unroll
-        for (int k = 0; k < 11; ++k)
+        for (int k = 0; k < NJ; ++k)
             if (tj + 16 * k < K) out[(size_t)(8 * ti + i) * K + tj + 16 * k] = acc1[i][k];
 #pragma unroll
-        for (int k = 0; k < 3; ++k)
+        for (int k = 0; k < NO; ++k)
             if (ti + 16 * k < O) out[(size_t)H * K + (size_t)(ti + 16 * k) * H + 8 * tj + i] = acc2[k][i];
         if (tj == 0) out[(size_t)H * K + (size_t)O * H + 8 * ti + i] = accb[i];
     }
@@ -174,12 +177,31 @@ int npa_mlp_weight_grad(const float *z, const float *dh, const float *h, const f
     if (scratch_floats < need)
         return fail(NPA_ERR_SCRATCH_TOO_SMALL, "npa_mlp_weight_grad: scratch has %lld floats, %lld needed", (long long)scratch_floats, (long long)need);
     MlpGradArgs a = {z, dh, h, dy, rows, in_dim, out_dim, scratch, dW1, dW2, db1, mlp_grad_ctas(rows)};
-    const size_t smem = (size_t)2 * kMlpRows * (in_dim + 2 * kMlpHidden + out_dim) * sizeof(float);
-    // the limit belongs to the function on the current device; setting it on every call keeps no state
-    cudaError_t e = cudaFuncSetAttribute(mlp_weight_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_mlp_weight_grad: raising the shared-memory limit: %s", cudaGetErrorString(e));
+    const size_t smem = (size_t)2 * (kMlpRows * (in_dim + 2 * kMlpHidden + out_dim) + 16) * sizeof(float);
     cudaStream_t st = (cudaStream_t)stream;
-    mlp_weight_grad_kernel<<<a.ctas, kMlpThreads, smem, st>>>(a);
+    // columns per thread: the smallest instantiated widths that cover in_dim and out_dim
+    const int nj = (in_dim + 15) / 16, no = (out_dim + 15) / 16;
+    cudaError_t e = cudaSuccess;
+#define NPA_MLP_LAUNCH(NJ, NO)                                                                                      \
+    do {                                                                                                            \
+        e = cudaFuncSetAttribute(mlp_weight_grad_kernel<NJ, NO>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                 (int)smem);                                                                        \
+        if (e == cudaSuccess) mlp_weight_grad_kernel<NJ, NO><<<a.ctas, kMlpThreads, smem, st>>>(a);                 \
+    } while (0)
+#define NPA_MLP_PICK_NO(NJ)                                                                                         \
+    do {                                                                                                            \
+        if (no <= 1) NPA_MLP_LAUNCH(NJ, 1);                                                                         \
+        else if (no == 2) NPA_MLP_LAUNCH(NJ, 2);                                                                    \
+        else NPA_MLP_LAUNCH(NJ, 3);                                                                                 \
+    } while (0)
+    // the limit belongs to the function on the current device; setting it on every call keeps no state
+    if (nj <= 3) NPA_MLP_PICK_NO(3);
+    else if (nj <= 5) NPA_MLP_PICK_NO(5);
+    else if (nj <= 8) NPA_MLP_PICK_NO(8);
+    else NPA_MLP_PICK_NO(11);
+#undef NPA_MLP_PICK_NO
+#undef NPA_MLP_LAUNCH
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_mlp_weight_grad: raising the shared-memory limit: %s", cudaGetErrorString(e));
     int rc = check_launch("mlp_weight_grad_kernel");
     if (rc != NPA_OK) return rc;
     const int total = kMlpHidden * in_dim + out_dim * kMlpHidden + kMlpHidden;
