@@ -23,8 +23,9 @@ from .workloads import CONFIGS
 
 
 def _time(fn, sets, reps):
-    for t in sets:
-        fn(t)
+    for _ in range(3):  # warm-up: kernels, launch sizes, and the caching allocator's pools
+        for t in sets:
+            fn(t)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

@@ -2,9 +2,10 @@
 
 The reference's MLP (models/npa.py:63-75) is ``Linear(in, hidden) -> ReLU -> Linear(hidden, out,
 bias=False)`` applied to every particle.  Its two forward GEMMs and the two input-gradient GEMMs
-stay library calls (torch / cuBLAS, fp32); the gradients of the weights -- three reductions over
-all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one kernel
-(``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` with that backward when
+run on the tensor cores at fp32 accuracy (``npa_linear_tf32x3``: three TF32 MMAs per product on
+split operands, bias and ReLU in the epilogue); the gradients of the weights -- three reductions
+over all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one
+CUDA-core kernel (``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` with that backward when
 ``module`` has the reference's structure and a hidden width of 128, and plain ``module(z)``
 otherwise.
 """
@@ -17,14 +18,34 @@ from . import _native as N
 _lib = N.lib
 HIDDEN = 128
 MAX_IN, MAX_OUT = 176, 48
+MIN_TENSOR_DIM = 64   # narrower products go to the library
+
+
+def _linear(a, w, bias, relu, w_is_out_by_in):
+    """``a @ w.T`` (``w`` is [out, in], as in F.linear) or ``a @ w`` (``w`` is [in, out]) with optional
+    bias and ReLU on the tensor cores (three TF32 MMAs per product, fp32 accuracy)."""
+    m, k = a.shape
+    n = w.shape[0] if w_is_out_by_in else w.shape[1]
+    if min(k, n) < MIN_TENSOR_DIM:
+        # thin products (35 output or input columns) are bound by memory and launch latency, not by
+        # arithmetic: the library's fp32 kernels are faster there
+        wt = w.t() if w_is_out_by_in else w
+        c = torch.addmm(bias, a, wt) if bias is not None else a @ wt
+        return c.relu_() if relu else c
+    stride_out, stride_in = (w.stride(0), w.stride(1)) if w_is_out_by_in else (w.stride(1), w.stride(0))
+    c = torch.empty(m, n, dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        N.check(_lib.npa_linear_tf32x3(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(c), m, k, n, stride_out, stride_in,
+                                       1 if relu else 0, N.current_stream()))
+    return c
 
 
 class _AdaptationMLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, z, w1, b1, w2):
         rows = z.reshape(-1, z.shape[-1])
-        h = torch.addmm(b1, rows, w1.t()).relu_()
-        y = h @ w2.t()
+        h = _linear(rows, w1, b1, True, True)
+        y = _linear(h, w2, None, False, True)
         ctx.save_for_backward(rows, h, w1, w2)
         ctx.z_shape = z.shape
         return y.reshape(*z.shape[:-1], w2.shape[0])
@@ -34,8 +55,8 @@ class _AdaptationMLP(torch.autograd.Function):
         rows, h, w1, w2 = ctx.saved_tensors
         need_z, need_w1, need_b1, need_w2 = ctx.needs_input_grad
         dy = g_y.reshape(-1, g_y.shape[-1]).contiguous()
-        dh = torch.ops.aten.threshold_backward(dy @ w2, h, 0.0)   # ReLU mask from the saved activations
-        g_z = (dh @ w1).reshape(ctx.z_shape) if need_z else None
+        dh = torch.ops.aten.threshold_backward(_linear(dy, w2, None, False, False), h, 0.0)  # ReLU mask
+        g_z = _linear(dh, w1, None, False, False).reshape(ctx.z_shape) if need_z else None
         g_w1 = g_b1 = g_w2 = None
         if need_w1 or need_b1 or need_w2:
             m, k, o = rows.shape[0], rows.shape[1], w2.shape[0]

@@ -204,3 +204,14 @@ def test_mlp_weight_grad_rejects_unsupported_shapes_before_any_launch():
     assert call(1000, 66, 128, 49) == n.NPA_ERR_UNSUPPORTED
     assert call(0, 66, 128, 18) == n.NPA_ERR_INVALID_ARGUMENT
     assert call(1000, 66, 128, 18, scratch_floats=10) == n.NPA_ERR_SCRATCH_TOO_SMALL
+
+
+def test_linear_tf32x3_rejects_unsupported_shapes_before_any_launch():
+    from npa_b200 import _native as n
+    buf, null = ctypes.c_void_p(256), ctypes.c_void_p(0)
+    call = lambda rows, k, o, a=buf: n.lib.npa_linear_tf32x3(a, buf, null, buf, rows, k, o, k, 1, 0, null)
+    assert call(1000, 177, 128) == n.NPA_ERR_UNSUPPORTED
+    assert call(1000, 128, 200) == n.NPA_ERR_UNSUPPORTED
+    assert call(1000, 176, 176) == n.NPA_ERR_UNSUPPORTED and "shared memory" in n.last_error()
+    assert call(0, 128, 128) == n.NPA_ERR_INVALID_ARGUMENT
+    assert call(1000, 128, 128, null) == n.NPA_ERR_INVALID_ARGUMENT

@@ -1,6 +1,6 @@
-"""The adaptation MLP with the fused weight-gradient kernel (npa_mlp_weight_grad, npa_b200.mlp)
-against torch autograd: same forward values, gradients held to float64 truth no worse than torch's
-own float32 backward."""
+"""The adaptation MLP on the tensor-core linear kernel (npa_linear_tf32x3: three TF32 MMAs per
+product) and the fused weight-gradient kernel (npa_mlp_weight_grad) against torch: values and
+gradients held to float64 truth about as tightly as torch's own float32 run."""
 import pytest
 import torch
 
@@ -37,9 +37,9 @@ def test_gradients_match_float64_truth(rows, k, o):
         scale = float(t.abs().max())
         err_ours = float((a.double() - t).abs().max())
         err_torch = float((b.double() - t).abs().max())
-        assert err_ours <= 2 * err_torch + 2e-6 * scale, (name, err_ours, err_torch, scale)
-    # the forward and the input gradient are the same library calls: identical bits
-    assert torch.equal(ours[0], theirs[0])
+        # the split-precision products drop a term of 2^-22 per product: allow a few fp32 roundings more
+        assert err_ours <= 4 * err_torch + 4e-6 * scale, (name, err_ours, err_torch, scale)
+        print(f"{name}: error {err_ours:.3e} (torch fp32 {err_torch:.3e}) at scale {scale:.3e}")
 
 
 def test_two_runs_are_bit_identical_and_unsupported_shapes_fall_back():
@@ -61,3 +61,26 @@ def test_two_runs_are_bit_identical_and_unsupported_shapes_fall_back():
     assert zr.grad is not None and wide[0].weight.grad is not None
     big = _mlp(200, 18)
     assert not supported(big)
+
+
+@pytest.mark.parametrize("rows,k,n,out_by_in,relu,bias", [(1000, 163, 128, True, True, True), (777, 128, 35, True, False, False),
+                                                          (4096, 35, 128, False, False, False), (130, 128, 163, False, False, False),
+                                                          (64, 176, 128, True, True, True), (5, 3, 1, True, False, True)])
+def test_linear_kernel_against_float64(rows, k, n, out_by_in, relu, bias):
+    """npa_linear_tf32x3 alone, both weight layouts, odd sizes, partial tiles."""
+    from npa_b200.mlp import _linear
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.randn(rows, k, generator=g, device="cuda")
+    w = torch.randn((n, k) if out_by_in else (k, n), generator=g, device="cuda")
+    b = torch.randn(n, generator=g, device="cuda") if bias else None
+    got = _linear(a, w, b, relu, out_by_in)
+    want = a.double() @ (w.double().t() if out_by_in else w.double())
+    if bias:
+        want = want + b.double()
+    if relu:
+        want = want.relu()
+    plain = (a @ (w.t() if out_by_in else w)) + (b if bias else 0)
+    plain = plain.relu() if relu else plain
+    scale = float(want.abs().max())
+    err, err_torch = float((got.double() - want).abs().max()), float((plain.double() - want).abs().max())
+    assert err <= 4 * err_torch + 4e-6 * scale, (err, err_torch, scale)
