@@ -1,13 +1,13 @@
-"""The per-particle adaptation MLP of an NPA model with a fused weight-gradient pass.
+"""The per-particle adaptation MLP of an NPA model: tensor-core linear layers, fused weight gradients.
 
 The reference's MLP (models/npa.py:63-75) is ``Linear(in, hidden) -> ReLU -> Linear(hidden, out,
 bias=False)`` applied to every particle.  Its two forward GEMMs and the two input-gradient GEMMs
 run on the tensor cores at fp32 accuracy (``npa_linear_tf32x3``: three TF32 MMAs per product on
 split operands, bias and ReLU in the epilogue); the gradients of the weights -- three reductions
 over all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one
-CUDA-core kernel (``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` with that backward when
-``module`` has the reference's structure and a hidden width of 128, and plain ``module(z)``
-otherwise.
+CUDA-core kernel (``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` computed
+this way when ``module`` has the reference's structure and a hidden width of 128, and plain
+``module(z)`` otherwise.
 """
 from __future__ import annotations
 
