@@ -418,15 +418,16 @@ int npa_mlp_weight_grad(const float *z, const float *dh, const float *h, const f
 
 /* ---- linear layers of the MLP on the tensor cores, fp32 accuracy ----------------- *
  *   C [rows, out] = act( A [rows, in] . B + bias ),  B[k][n] = W[n * w_stride_out + k * w_stride_in]
- * with act = ReLU when relu != 0; bias [out] may be NULL.  torch's F.linear(x, W) with
+ * with act = ReLU when relu != 0; bias [out] may be NULL; with gate [rows, out] != NULL the output
+ * is zero where gate <= 0 (the backward of a ReLU whose output is gate).  torch's F.linear(x, W) with
  * W [out, in] is (w_stride_out, w_stride_in) = (in, 1); x @ W with W [in, out] is (1, out).
  * Each product is three TF32 tensor-core MMAs on operands split into a TF32 head and tail
  * (fp32 accumulation), accurate to ~1e-6 relative.  in, out <= 176 and the weights must fit in
  * shared memory with two 64-row tiles of A (else NPA_ERR_UNSUPPORTED).  Replaces the four SIMT
  * fp32 GEMMs of the adaptation MLP (models/npa.py:63-75,143) and its bias / ReLU passes. */
-int npa_linear_tf32x3(const float *A, const float *W, const float *bias, float *C, int64_t rows,
-                      int32_t in_dim, int32_t out_dim, int64_t w_stride_out, int64_t w_stride_in,
-                      int32_t relu, void *stream);
+int npa_linear_tf32x3(const float *A, const float *W, const float *bias, const float *gate, float *C,
+                      int64_t rows, int32_t in_dim, int32_t out_dim, int64_t w_stride_out,
+                      int64_t w_stride_in, int32_t relu, void *stream);
 
 #ifdef __cplusplus
 }

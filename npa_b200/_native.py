@@ -83,7 +83,7 @@ SIGNATURES = {
     "npa_mlp_weight_grad_scratch_floats": (ctypes.c_int64, [ctypes.c_int64, _I32, _I32]),
     "npa_mlp_weight_grad": (ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int64, _I32, _I32, _I32, _P, ctypes.c_int64,
                                            _P, _P, _P, _P]),
-    "npa_linear_tf32x3": (ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
+    "npa_linear_tf32x3": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
                                          _I32, _P]),
     "npa_step_update_backward": (ctypes.c_int, [_P] * 3 + [_I32, ctypes.c_float, ctypes.c_float, _P, _P, _P, _P]),
 }

@@ -29,6 +29,7 @@ struct GemmArgs {
     const float *A;      // [M, K], row pitch K
     const float *W;      // weights, addressed through the two strides
     const float *bias;   // [N] or NULL
+    const float *gate;   // [M, N] or NULL: the output is zero where gate <= 0 (ReLU backward)
     float *C;            // [M, N], row pitch N
     long long M;
     int K, N, stride_n, stride_k, relu;
@@ -148,8 +149,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_tf32x3_kernel(GemmArgs
                         const float bv = a.bias ? __ldg(a.bias + c) : 0.f;
                         float v0 = acc[j][q] + bv, v1 = acc[j][2 + q] + bv;
                         if (a.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-                        if (row_a < a.M) a.C[row_a * N + c] = v0;
-                        if (row_b < a.M) a.C[row_b * N + c] = v1;
+                        if (row_a < a.M) a.C[row_a * N + c] = (a.gate && !(__ldg(a.gate + row_a * N + c) > 0.f)) ? 0.f : v0;
+                        if (row_b < a.M) a.C[row_b * N + c] = (a.gate && !(__ldg(a.gate + row_b * N + c) > 0.f)) ? 0.f : v1;
                     }
                 }
             }
@@ -164,8 +165,9 @@ using namespace npa;
 
 extern "C" {
 
-int npa_linear_tf32x3(const float *A, const float *W, const float *bias, float *C, int64_t rows, int32_t in_dim,
-                      int32_t out_dim, int64_t w_stride_out, int64_t w_stride_in, int32_t relu, void *stream) {
+int npa_linear_tf32x3(const float *A, const float *W, const float *bias, const float *gate, float *C, int64_t rows,
+                      int32_t in_dim, int32_t out_dim, int64_t w_stride_out, int64_t w_stride_in, int32_t relu,
+                      void *stream) {
     if (rows <= 0 || in_dim <= 0 || out_dim <= 0)
         return fail(NPA_ERR_INVALID_ARGUMENT, "npa_linear_tf32x3: rows, in_dim and out_dim must be positive");
     if (in_dim > kGemmMaxDim || out_dim > kGemmMaxDim)
@@ -174,7 +176,7 @@ int npa_linear_tf32x3(const float *A, const float *W, const float *bias, float *
     if (!A || !W || !C) return fail(NPA_ERR_INVALID_ARGUMENT, "npa_linear_tf32x3: A, W and C must be non-NULL");
     if ((uintptr_t)A % 4 || (uintptr_t)C % 4) return fail(NPA_ERR_INVALID_ARGUMENT, "npa_linear_tf32x3: A and C must be float aligned");
     GemmArgs a = {};
-    a.A = A; a.W = W; a.bias = bias; a.C = C; a.M = rows; a.K = in_dim; a.N = out_dim;
+    a.A = A; a.W = W; a.bias = bias; a.gate = gate; a.C = C; a.M = rows; a.K = in_dim; a.N = out_dim;
     a.stride_n = (int)w_stride_out; a.stride_k = (int)w_stride_in; a.relu = relu;
     a.Kp = (in_dim + 7) / 8 * 8;
     a.lda = a.Kp + 4;

@@ -19,23 +19,27 @@ _lib = N.lib
 HIDDEN = 128
 MAX_IN, MAX_OUT = 176, 48
 MIN_TENSOR_DIM = 64   # narrower products go to the library
+GATED_DH_ON_TENSOR_CORES = False  # dh = (dy W2) gated by h in one tensor-core kernel: measured slower (1.42 vs 1.35 ms per MLP pass) than the thin library GEMM + a mask pass
 
 
-def _linear(a, w, bias, relu, w_is_out_by_in):
+def _linear(a, w, bias, relu, w_is_out_by_in, gate=None, force_tensor=False):
     """``a @ w.T`` (``w`` is [out, in], as in F.linear) or ``a @ w`` (``w`` is [in, out]) with optional
-    bias and ReLU on the tensor cores (three TF32 MMAs per product, fp32 accuracy)."""
+    bias and ReLU on the tensor cores (three TF32 MMAs per product, fp32 accuracy); with ``gate`` the
+    result is zeroed where ``gate <= 0`` (the backward of the ReLU that produced ``gate``)."""
     m, k = a.shape
     n = w.shape[0] if w_is_out_by_in else w.shape[1]
-    if min(k, n) < MIN_TENSOR_DIM:
+    if min(k, n) < MIN_TENSOR_DIM and not force_tensor:
         # thin products (35 output or input columns) are bound by memory and launch latency, not by
         # arithmetic: the library's fp32 kernels are faster there
         wt = w.t() if w_is_out_by_in else w
         c = torch.addmm(bias, a, wt) if bias is not None else a @ wt
+        if gate is not None:
+            c = torch.ops.aten.threshold_backward(c, gate, 0.0)
         return c.relu_() if relu else c
     stride_out, stride_in = (w.stride(0), w.stride(1)) if w_is_out_by_in else (w.stride(1), w.stride(0))
     c = torch.empty(m, n, dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
-        N.check(_lib.npa_linear_tf32x3(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(c), m, k, n, stride_out, stride_in,
+        N.check(_lib.npa_linear_tf32x3(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(gate), N.ptr(c), m, k, n, stride_out, stride_in,
                                        1 if relu else 0, N.current_stream()))
     return c
 
@@ -55,7 +59,7 @@ class _AdaptationMLP(torch.autograd.Function):
         rows, h, w1, w2 = ctx.saved_tensors
         need_z, need_w1, need_b1, need_w2 = ctx.needs_input_grad
         dy = g_y.reshape(-1, g_y.shape[-1]).contiguous()
-        dh = torch.ops.aten.threshold_backward(_linear(dy, w2, None, False, False), h, 0.0)  # ReLU mask
+        dh = _linear(dy, w2, None, False, False, gate=h, force_tensor=GATED_DH_ON_TENSOR_CORES)  # ReLU mask from h
         g_z = _linear(dh, w1, None, False, False).reshape(ctx.z_shape) if need_z else None
         g_w1 = g_b1 = g_w2 = None
         if need_w1 or need_b1 or need_w2:

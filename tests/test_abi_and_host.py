@@ -209,7 +209,7 @@ def test_mlp_weight_grad_rejects_unsupported_shapes_before_any_launch():
 def test_linear_tf32x3_rejects_unsupported_shapes_before_any_launch():
     from npa_b200 import _native as n
     buf, null = ctypes.c_void_p(256), ctypes.c_void_p(0)
-    call = lambda rows, k, o, a=buf: n.lib.npa_linear_tf32x3(a, buf, null, buf, rows, k, o, k, 1, 0, null)
+    call = lambda rows, k, o, a=buf: n.lib.npa_linear_tf32x3(a, buf, null, null, buf, rows, k, o, k, 1, 0, null)
     assert call(1000, 177, 128) == n.NPA_ERR_UNSUPPORTED
     assert call(1000, 128, 200) == n.NPA_ERR_UNSUPPORTED
     assert call(1000, 176, 176) == n.NPA_ERR_UNSUPPORTED and "shared memory" in n.last_error()

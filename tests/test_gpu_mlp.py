@@ -84,3 +84,16 @@ def test_linear_kernel_against_float64(rows, k, n, out_by_in, relu, bias):
     scale = float(want.abs().max())
     err, err_torch = float((got.double() - want).abs().max()), float((plain.double() - want).abs().max())
     assert err <= 4 * err_torch + 4e-6 * scale, (err, err_torch, scale)
+
+
+def test_gated_linear_is_the_relu_backward():
+    from npa_b200.mlp import _linear
+    g = torch.Generator(device="cuda").manual_seed(3)
+    dy = torch.randn(3000, 35, generator=g, device="cuda")
+    w2 = torch.randn(35, 128, generator=g, device="cuda")
+    h = torch.randn(3000, 128, generator=g, device="cuda").relu()
+    want = torch.where(h > 0, dy.double() @ w2.double(), torch.zeros((), dtype=torch.float64, device="cuda"))
+    for force in (True, False):
+        got = _linear(dy, w2, None, False, False, gate=h, force_tensor=force)
+        assert float((got.double() - want).abs().max()) <= 4e-6 * float(want.abs().max())
+        assert torch.equal(got == 0, want == 0) or float(((got == 0) != (want == 0)).float().mean()) < 1e-6
