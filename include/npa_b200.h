@@ -78,7 +78,7 @@ int64_t npa_grid_num_cells(const npa_grid *g);
  * (sph_cuda.cu:1851-1853).  Unlike the reference, the same size is used with
  * the Morton hash, because the work list drives every kernel here. */
 int64_t npa_grid_max_blocks(const npa_grid *g);
-/* Bytes of device scratch npa_grid_build() needs (cell histogram, cursors,
+/* Bytes of device scratch npa_grid_build() needs (cell histogram, arrival numbers,
  * cell ids, unsorted slots, scan partials); replaces the cudaMalloc'ed members
  * of the reference's HashGrid (sph_cuda.cu:1881-1895). */
 int64_t npa_grid_scratch_bytes(const npa_grid *g);

@@ -27,11 +27,11 @@ constexpr int kScanTile = kScanThreads * kScanPerThread;
 
 struct BinScratch {
     uint32_t *counts;   // [B*cells + 1]
-    uint32_t *cursor;   // [B*cells]
+    uint32_t *arrive;   // [B*N]  arrival number of the particle inside its cell (any order)
     uint32_t *cellid;   // [B*N]
     uint32_t *order;    // [B*N]  slot -> particle, unsorted inside a cell
     unsigned long long *partials;  // [tiles + 1] packed (blocks << 32 | particles)
-    size_t zero_bytes;  // counts + cursor are contiguous and zeroed per call
+    size_t zero_bytes;  // the counts are zeroed per call
     int tiles;
 };
 
@@ -45,9 +45,9 @@ static size_t layout_scratch(const Geom &g, void *base, BinScratch *s) {
     char *p = (char *)base;
     size_t counts_off = off;
     off += align_up((nc + 1) * 4);
-    size_t cursor_off = off;
-    off += align_up(nc * 4);
     size_t zero_end = off;
+    size_t arrive_off = off;
+    off += align_up(np * 4);
     size_t cellid_off = off;
     off += align_up(np * 4);
     size_t order_off = off;
@@ -56,7 +56,7 @@ static size_t layout_scratch(const Geom &g, void *base, BinScratch *s) {
     off += align_up((size_t)(tiles + 1) * 8);
     if (s) {
         s->counts = (uint32_t *)(p + counts_off);
-        s->cursor = (uint32_t *)(p + cursor_off);
+        s->arrive = (uint32_t *)(p + arrive_off);
         s->cellid = (uint32_t *)(p + cellid_off);
         s->order = (uint32_t *)(p + order_off);
         s->partials = (unsigned long long *)(p + part_off);
@@ -85,19 +85,24 @@ __device__ inline uint32_t particle_cell(const float *__restrict__ x, size_t idx
     return cell_hash<D>(g, cx, cy, cz);
 }
 
-// One atomic per distinct cell per warp: lanes holding the same key elect
-// their lowest lane, which adds the group's population.
-__device__ inline void warp_aggregated_inc(uint32_t *hist, uint32_t key, bool valid) {
-    unsigned mask = __ballot_sync(kFull, valid);
-    if (!valid) return;
-    unsigned peers = __match_any_sync(mask, key);
-    int lane = threadIdx.x & 31;
-    if ((peers & ((1u << lane) - 1)) == 0) atomicAdd(&hist[key], (uint32_t)__popc(peers));
+// One atomic per distinct cell per warp: lanes holding the same key elect their lowest lane, which
+// adds the group's population; every lane gets its arrival number in the cell (the counter's old
+// value plus its rank in the group), which later serves as its unsorted slot inside the cell.
+__device__ inline uint32_t warp_aggregated_take(uint32_t *hist, uint32_t key, bool valid) {
+    const unsigned mask = __ballot_sync(kFull, valid);
+    if (!valid) return 0;
+    const unsigned peers = __match_any_sync(mask, key);
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(peers) - 1;
+    uint32_t base = 0;
+    if (lane == leader) base = atomicAdd(&hist[key], (uint32_t)__popc(peers));
+    base = __shfl_sync(peers, base, leader);
+    return base + (uint32_t)__popc(peers & ((1u << lane) - 1));
 }
 
 template <int D, bool SMEM>
 __global__ void __launch_bounds__(kBinThreads)
-hash_count_kernel(const float *__restrict__ x, uint32_t *__restrict__ cellid,
+hash_count_kernel(const float *__restrict__ x, uint32_t *__restrict__ cellid, uint32_t *__restrict__ arrive,
                   uint32_t *__restrict__ counts, Geom g) {
     extern __shared__ uint32_t hist[];
     const int b = blockIdx.y;
@@ -107,6 +112,7 @@ hash_count_kernel(const float *__restrict__ x, uint32_t *__restrict__ cellid,
         __syncthreads();
     }
     uint32_t *gl = counts + (size_t)b * g.cells;
+    uint32_t keys[kBinPerThread], arr[kBinPerThread];
 #pragma unroll
     for (int k = 0; k < kBinPerThread; ++k) {
         const int i = base + k * kBinThreads + threadIdx.x;
@@ -117,14 +123,23 @@ hash_count_kernel(const float *__restrict__ x, uint32_t *__restrict__ cellid,
             key = particle_cell<D>(x, idx, g);
             cellid[idx] = key;
         }
-        warp_aggregated_inc(SMEM ? hist : gl, key, valid);
+        keys[k] = key;
+        arr[k] = warp_aggregated_take(SMEM ? hist : gl, key, valid);
     }
     if (SMEM) {
+        // the CTA's populations go to the global counters in one atomic per cell; the old values
+        // (where this CTA's particles start in the cell) replace the local counts
         __syncthreads();
         for (int c = threadIdx.x; c < g.cells; c += kBinThreads) {
-            uint32_t v = hist[c];
-            if (v) atomicAdd(&gl[c], v);
+            const uint32_t v = hist[c];
+            hist[c] = v ? atomicAdd(&gl[c], v) : 0u;
         }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int k = 0; k < kBinPerThread; ++k) {
+        const int i = base + k * kBinThreads + threadIdx.x;
+        if (i < g.N) arrive[(size_t)b * g.N + i] = arr[k] + (SMEM ? hist[keys[k]] : 0u);
     }
 }
 
@@ -241,23 +256,14 @@ scan_apply_kernel(const uint32_t *__restrict__ counts, const unsigned long long 
 // cell), then rank each slot by original index -> stable permutation.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kBinThreads)
-scatter_kernel(const uint32_t *__restrict__ cellid, const int32_t *__restrict__ bin_offsets,
-               uint32_t *__restrict__ cursor, uint32_t *__restrict__ order, Geom g) {
+scatter_kernel(const uint32_t *__restrict__ cellid, const uint32_t *__restrict__ arrive,
+               const int32_t *__restrict__ bin_offsets, uint32_t *__restrict__ order, Geom g) {
     const int b = blockIdx.y;
     const int i = blockIdx.x * kBinThreads + threadIdx.x;
-    const bool valid = i < g.N;
-    const unsigned mask = __ballot_sync(kFull, valid);
-    if (!valid) return;
-    const uint32_t key = cellid[(size_t)b * g.N + i];
-    const unsigned peers = __match_any_sync(mask, key);
-    const int lane = threadIdx.x & 31;
-    const int leader = __ffs(peers) - 1;
-    uint32_t basev = 0;
-    const size_t cell = (size_t)b * g.cells + key;
-    if (lane == leader) basev = atomicAdd(&cursor[cell], (uint32_t)__popc(peers));
-    basev = __shfl_sync(peers, basev, leader);
-    const uint32_t slot = (uint32_t)bin_offsets[cell] + basev + (uint32_t)__popc(peers & ((1u << lane) - 1));
-    order[slot] = (uint32_t)i;
+    if (i >= g.N) return;
+    const size_t idx = (size_t)b * g.N + i;
+    const size_t cell = (size_t)b * g.cells + cellid[idx];
+    order[(uint32_t)bin_offsets[cell] + arrive[idx]] = (uint32_t)i;  // no atomics: the slot was drawn in pass 1
 }
 
 __global__ void __launch_bounds__(kBinThreads)
@@ -406,11 +412,11 @@ int npa_grid_build(const npa_grid *gd, const float *x, int32_t *permutation, int
     const bool smem = g.cells <= kSmemHistCells;
     const size_t smem_bytes = smem ? (size_t)g.cells * 4 : 0;
     if (g.dim == 2) {
-        if (smem) hash_count_kernel<2, true><<<pgrid, kBinThreads, smem_bytes, st>>>(x, s.cellid, s.counts, g);
-        else hash_count_kernel<2, false><<<pgrid, kBinThreads, 0, st>>>(x, s.cellid, s.counts, g);
+        if (smem) hash_count_kernel<2, true><<<pgrid, kBinThreads, smem_bytes, st>>>(x, s.cellid, s.arrive, s.counts, g);
+        else hash_count_kernel<2, false><<<pgrid, kBinThreads, 0, st>>>(x, s.cellid, s.arrive, s.counts, g);
     } else {
-        if (smem) hash_count_kernel<3, true><<<pgrid, kBinThreads, smem_bytes, st>>>(x, s.cellid, s.counts, g);
-        else hash_count_kernel<3, false><<<pgrid, kBinThreads, 0, st>>>(x, s.cellid, s.counts, g);
+        if (smem) hash_count_kernel<3, true><<<pgrid, kBinThreads, smem_bytes, st>>>(x, s.cellid, s.arrive, s.counts, g);
+        else hash_count_kernel<3, false><<<pgrid, kBinThreads, 0, st>>>(x, s.cellid, s.arrive, s.counts, g);
     }
     if ((rc = check_launch("hash_count_kernel")) != NPA_OK) return rc;
 
@@ -424,7 +430,7 @@ int npa_grid_build(const npa_grid *gd, const float *x, int32_t *permutation, int
     if ((rc = check_launch("scan_apply_kernel")) != NPA_OK) return rc;
 
     const dim3 tgrid((g.N + kBinThreads - 1) / kBinThreads, g.B);
-    scatter_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, bin_offsets, s.cursor, s.order, g);
+    scatter_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, s.arrive, bin_offsets, s.order, g);
     if ((rc = check_launch("scatter_kernel")) != NPA_OK) return rc;
     rank_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, bin_offsets, s.order, permutation, g);
     return check_launch("rank_kernel");
