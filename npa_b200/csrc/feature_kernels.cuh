@@ -28,13 +28,11 @@
 namespace npa {
 
 constexpr int kListPerWarp = 128;  // accepted-pair slots per warp
-constexpr int kFwdStages = 4;       // pairs fetched ahead per sub-group, forward
 constexpr int kBwdStages = 2;       // same, backward (five pieces per pair)
 // Full backward: smaller CTAs give the register allocator a finer occupancy grid (5 x 4 warps)
 constexpr int kBwdFullWarps = 4;
 constexpr int kBwdFullCtas = 5;
 constexpr int bwd_warps(bool full) { return full ? kBwdFullWarps : kWarpsPerCta; }
-constexpr bool kFwdRing = false;    // forward: cp.async ring (true) or three register sets (false)
 constexpr bool kBwdRing = true;     // backward: cp.async ring (true) or register double buffer (false)
 
 template <int VW>
@@ -141,19 +139,15 @@ template <int D, bool PER, int LPP, int VW, int MASK>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, (MASK & (F_MOMENT | F_PACK)) ? 3 : 4)
 feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     constexpr int PP = 32 / LPP;  // pairs drained in parallel
-    constexpr int S = kFwdStages;
     __shared__ int4 s_ranges[kWarpsPerCta][kMaxRanges];
     __shared__ float4 s_geo[kWarpsPerCta][kListPerWarp];  // r.x r.y r.z, index of j
     __shared__ float4 s_ent[kWarpsPerCta][kListPerWarp];  // v_j K.x, v_j K.y, v_j K.z, v_j W
-    extern __shared__ __align__(16) unsigned char s_dyn[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sg = lane / LPP, sl = lane % LPP;
     int4 *rng = s_ranges[warp];
     float4 *geo = s_geo[warp];
     float4 *ent = s_ent[warp];
-    // lane-private staging ring for the neighbour's feature piece: [stage][lane]
-    Piece<VW> *ring = reinterpret_cast<Piece<VW> *>(s_dyn) + (size_t)warp * S * 32 + lane;
     const int C = a.C;
 
     // persistent warps: consecutive rows go to the warps of one CTA, then to the next CTA
@@ -217,15 +211,8 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                 }
                 __syncwarp();
                 if (fvalid) {
-                    // stage 3: each sub-group drains every PP-th pair; the neighbour's features are
-                    // fetched S pairs ahead with cp.async into this lane's ring
-                    auto fetch = [&](int e, int slot) {
-                        if (e < n) {
-                            const int j = __float_as_int(geo[e].w);
-                            async_copy<VW * 4>(ring + slot * 32, a.s + ((long long)j * C + f0));
-                        }
-                        async_commit();
-                    };
+                    // stage 3: each sub-group drains every PP-th pair; the neighbour's feature rows pass
+                    // through three rotating register sets, the rows of the next two pairs in flight
                     auto consume = [&](int e, const float (&sj)[VW]) {
                         const float4 en = ent[e];
 #pragma unroll
@@ -239,24 +226,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                             }
                         }
                     };
-                    if (kFwdRing) {
-#pragma unroll
-                        for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
-                        int slot = 0;
-                        for (int e = sg; e < n; e += PP) {
-                            async_wait<S - 1>();
-                            const Piece<VW> pj = ring[slot * 32];
-                            float sj[VW];
-#pragma unroll
-                            for (int q = 0; q < VW; ++q) sj[q] = pj.v[q];
-                            consume(e, sj);
-                            // refill the slot only after its values were consumed by the arithmetic above
-                            fetch(e + S * PP, slot);
-                            slot = slot + 1 == S ? 0 : slot + 1;
-                        }
-                        async_wait<0>();
-                    } else {
-                        // three register sets, the rows of the next two pairs in flight
+                    {
                         auto load = [&](int e, float (&sj)[VW]) {
                             if (e < n) load_feat<VW>(a.s + ((long long)__float_as_int(geo[e].w) * C + f0), sj);
                         };
@@ -665,7 +635,7 @@ inline bool feature_rows_vectorisable(int C, const void *p0, const void *p1, con
 template <int VW, typename Kernel>
 int launch_feature_forward_mask(const Geom &g, Kernel kernel, const FeatureFwdArgs &a, cudaStream_t st) {
     const int threads = kWarpsPerCta * 32;
-    const size_t dyn = kFwdRing ? (size_t)kWarpsPerCta * kFwdStages * 32 * sizeof(Piece<VW>) : 0;
+    const size_t dyn = 0;
     int ctas = 0;
     int rc = persistent_ctas(kernel, threads, dyn, &ctas);
     if (rc != NPA_OK) return rc;
