@@ -4,7 +4,11 @@ Nothing in the product (``npa_b200/``) imports this package.  It holds
 
 * ``sph_oracle.c``: a C restatement (double accumulation, OpenMP over particles)
   of the reference's pure-torch operators ``sphops/torch_sph.py``, loaded here
-  through ctypes (:func:`forward`, :func:`backward`, :func:`safe_inv_sym_mat`);
+  through ctypes (:func:`forward`, :func:`backward`, :func:`safe_inv_sym_mat`).
+  The same file built with ``-DORACLE_FP32`` evaluates every sum in float
+  (``precision="f32"``): the stand-in for the reference's own fp32 run where no
+  stored fp32 output exists, used only to size the "no worse than twice the
+  reference's fp32 error" clause of the parity gate;
 * ``binning.py``: a numpy restatement of the reference's cell hashing and of a
   stable counting sort (:mod:`oracle.binning`).
 
@@ -23,7 +27,9 @@ import numpy as np
 _DIR = Path(__file__).resolve().parent
 _SRC = _DIR / "sph_oracle.c"
 _LIB = _DIR / "libsph_oracle.so"
+_LIB32 = _DIR / "libsph_oracle_f32.so"
 _lib = None
+_lib32 = None
 
 
 class _Cfg(ctypes.Structure):
@@ -40,24 +46,34 @@ class _Cfg(ctypes.Structure):
 
 
 def build(force: bool = False) -> Path:
-    """Compile ``sph_oracle.c`` into ``oracle/libsph_oracle.so`` with gcc."""
-    if force or not _LIB.exists() or _LIB.stat().st_mtime < _SRC.stat().st_mtime:
-        cmd = ["gcc", "-O2", "-fopenmp", "-shared", "-fPIC", "-o", str(_LIB), str(_SRC), "-lm"]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"gcc failed on {_SRC.name}:\n{res.stderr}")
+    """Compile ``sph_oracle.c`` with gcc into ``oracle/libsph_oracle.so`` (double sums) and
+    ``oracle/libsph_oracle_f32.so`` (float sums, no fused multiply-adds)."""
+    for lib, extra in ((_LIB, []), (_LIB32, ["-DORACLE_FP32", "-ffp-contract=off"])):
+        if force or not lib.exists() or lib.stat().st_mtime < _SRC.stat().st_mtime:
+            cmd = ["gcc", "-O2", "-fopenmp", "-shared", "-fPIC", *extra, "-o", str(lib), str(_SRC), "-lm"]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"gcc failed on {_SRC.name}:\n{res.stderr}")
     return _LIB
 
 
-def _load():
-    global _lib
+def _open(path):
+    lib = ctypes.CDLL(str(path))
+    lib.oracle_forward.restype = ctypes.c_int
+    lib.oracle_backward.restype = ctypes.c_int
+    lib.oracle_num_threads.restype = ctypes.c_int
+    return lib
+
+
+def _load(precision: str = "f64"):
+    global _lib, _lib32
+    if precision not in ("f64", "f32"):
+        raise ValueError(f"precision must be 'f64' or 'f32', got {precision!r}")
     if _lib is None:
         build()
-        _lib = ctypes.CDLL(str(_LIB))
-        _lib.oracle_forward.restype = ctypes.c_int
-        _lib.oracle_backward.restype = ctypes.c_int
-        _lib.oracle_num_threads.restype = ctypes.c_int
-    return _lib
+        _lib = _open(_LIB)
+        _lib32 = _open(_LIB32)
+    return _lib if precision == "f64" else _lib32
 
 
 def num_threads() -> int:
@@ -66,6 +82,7 @@ def num_threads() -> int:
 
 def set_threads(n: int) -> None:
     _load().oracle_set_threads(ctypes.c_int(int(n)))
+    _load("f32").oracle_set_threads(ctypes.c_int(int(n)))
 
 
 def _f32(a):
@@ -90,15 +107,16 @@ def _cfg(x, dim, h, periodic, box_size, channels):
 
 
 def forward(x, h, dim, *, mass=None, s=None, rho_in=None, periodic=False, box_size=None,
-            want=("rho",)):
+            want=("rho",), precision="f64"):
     """Run the C oracle forward.
 
     ``x`` is ``[B, N, P]`` (P >= dim; extra columns ignored), ``want`` names the
     outputs to compute out of ``count, rho, rho_grad, blur, grad, moment``.
     ``rho_in`` is the density handed to blur / grad / moment (their ``rho``
-    argument).  Returns a dict of numpy arrays (``count`` float32, others float64).
+    argument).  ``precision="f32"`` runs the float build.  Returns a dict of numpy arrays
+    (``count`` float32, others float64).
     """
-    lib = _load()
+    lib = _load(precision)
     x = _f32(x)
     B, N, _ = x.shape
     s = _f32(s)
@@ -121,10 +139,10 @@ def forward(x, h, dim, *, mass=None, s=None, rho_in=None, periodic=False, box_si
 
 
 def backward(x, h, dim, *, mass=None, s=None, rho_in=None, periodic=False, box_size=None,
-             g_rho=None, g_rho_grad=None, g_blur=None, g_grad=None, g_moment=None):
+             g_rho=None, g_rho_grad=None, g_blur=None, g_grad=None, g_moment=None, precision="f64"):
     """Run the C oracle backward (each operator differentiated independently, ``rho_in``
     treated as an input).  Returns ``dx [B,N,dim]``, ``ds [B,N,C]`` (or None) and ``drho [B,N]``."""
-    lib = _load()
+    lib = _load(precision)
     x = _f32(x)
     B, N, _ = x.shape
     s = _f32(s)

@@ -30,6 +30,24 @@
 #include <omp.h>
 #endif
 
+/* Arithmetic type of the sums.  The default build accumulates in double (the parity truth).
+ * Built with -DORACLE_FP32 every product, sum, square root and wrap below runs in float, in the
+ * same order: a plain fp32 evaluation of the same formulas, the stand-in for the reference's own
+ * fp32 run (torch_sph.py on float tensors) where no stored fp32 output exists.  Outputs are
+ * handed back as double arrays in both builds. */
+#ifdef ORACLE_FP32
+typedef float real;
+#define R_SQRT sqrtf
+#define R_FMOD fmodf
+#define R_FLOOR floorf
+#else
+typedef double real;
+#define R_SQRT sqrt
+#define R_FMOD fmod
+#define R_FLOOR floor
+#endif
+#define RC(x) ((real)(x))
+
 typedef struct oracle_cfg {
     int32_t dim;        /* 2 or 3 */
     int32_t pos_stride; /* floats per position in memory: 2, 3 or 4 */
@@ -58,19 +76,20 @@ void oracle_set_threads(int n) {
 }
 
 /* torch_sph.py:96-104 smoothing_poly6_normalization */
-static double poly6_norm(double h, int dim) {
-    return dim == 2 ? 4.0 / (M_PI * pow(h, 8.0)) : 315.0 / (64.0 * M_PI * pow(h, 9.0));
+static real poly6_norm(double h, int dim) {
+    return RC(dim == 2 ? 4.0 / (M_PI * pow(h, 8.0)) : 315.0 / (64.0 * M_PI * pow(h, 9.0)));
 }
 /* torch_sph.py:130-138 gradient_spiky_normalization */
-static double spiky_norm(double h, int dim) {
-    return dim == 2 ? 10.0 / (M_PI * pow(h, 5.0)) : 15.0 / (M_PI * pow(h, 6.0));
+static real spiky_norm(double h, int dim) {
+    return RC(dim == 2 ? 10.0 / (M_PI * pow(h, 5.0)) : 15.0 / (M_PI * pow(h, 6.0)));
 }
 
 /* torch.remainder(r + L/2, L) - L/2, torch_sph.py:41-52 */
-static double wrap(double r, double L) {
-    double t = fmod(r + 0.5 * L, L);
-    if (t < 0.0) t += L;
-    return t - 0.5 * L;
+static real wrap(real r, real L) {
+    const real half = RC(0.5) * L;
+    real t = R_FMOD(r + half, L);
+    if (t < RC(0.0)) t += L;
+    return t - half;
 }
 
 /* ---- private cell list --------------------------------------------------- */
@@ -176,11 +195,11 @@ static void free_cells(cell_list *cl) {
     } while (0)
 
 /* r = x_j - x_i (wrapped when periodic), torch_sph.py:24-53 */
-static double pair_r(const oracle_cfg *c, const float *xi, const float *xj, double *r) {
-    double q = 0.0;
+static real pair_r(const oracle_cfg *c, const float *xi, const float *xj, real *r) {
+    real q = RC(0.0);
     for (int d = 0; d < c->dim; ++d) {
-        double v = (double)xj[d] - (double)xi[d];
-        if (c->periodic) v = wrap(v, c->box[d]);
+        real v = RC(xj[d]) - RC(xi[d]);
+        if (c->periodic) v = wrap(v, RC(c->box[d]));
         r[d] = v;
         q += v * v;
     }
@@ -212,14 +231,14 @@ static float pair_q_f32(const oracle_cfg *c, const float *xi, const float *xj) {
 /* spiky magnitude and its derivative, torch_sph.py:140-162:
  *   d = sqrt(q), d_safe = sqrt(q + 1e-12), mask = d < h && d > 0,
  *   mag = 3 clamp(h - d_safe, 0)^2 / d_safe                      */
-static int spiky(double q, double h, double *phi, double *psi) {
-    double d = sqrt(q);
-    if (!(d < h) || !(d > 0.0)) return 0;
-    double ds = sqrt(q + 1e-12);
-    double t = h - ds;
-    if (t < 0.0) t = 0.0;
-    *phi = 3.0 * t * t / ds;
-    if (psi) *psi = 3.0 * t * (h + ds) / (ds * ds * ds); /* -(d phi / d ds) / ds */
+static int spiky(real q, real h, real *phi, real *psi) {
+    real d = R_SQRT(q);
+    if (!(d < h) || !(d > RC(0.0))) return 0;
+    real ds = R_SQRT(q + RC(1e-12));
+    real t = h - ds;
+    if (t < RC(0.0)) t = RC(0.0);
+    *phi = RC(3.0) * t * t / ds;
+    if (psi) *psi = RC(3.0) * t * (h + ds) / (ds * ds * ds); /* -(d phi / d ds) / ds */
     return 1;
 }
 
@@ -238,9 +257,9 @@ int oracle_forward(const oracle_cfg *c, const float *x, const float *mass, const
                    const float *rho_in, float *count, double *rho, double *rho_grad, double *blur,
                    double *grad, double *moment) {
     const int N = c->particles, D = c->dim, C = c->channels, P = c->pos_stride;
-    const double h = c->h, h2 = h * h;
-    const float h2f = (float)(h * h);
-    const double cs = poly6_norm(h, D), cg = spiky_norm(h, D);
+    const real h = RC(c->h), h2 = RC(c->h * c->h);
+    const float h2f = (float)(c->h * c->h);
+    const real cs = poly6_norm(c->h, D), cg = spiky_norm(c->h, D);
     if ((blur || grad || moment) && !rho_in) return -1;
     if ((blur || grad) && (!s || C <= 0)) return -1;
     for (int b = 0; b < c->batch; ++b) {
@@ -254,37 +273,38 @@ int oracle_forward(const oracle_cfg *c, const float *x, const float *mass, const
         for (int i = 0; i < N; ++i) {
             const float *xi = xb + (size_t)i * P;
             const size_t gi = (size_t)b * N + i;
-            double a_rho = 0.0, a_dg[3] = {0, 0, 0}, a_m[9] = {0};
+            real a_rho = RC(0.0), a_dg[3] = {0, 0, 0}, a_m[9] = {0};
             float a_cnt = 0.0f;
-            double *ob = blur ? blur + gi * C : NULL;
-            double *og = grad ? grad + gi * C * D : NULL;
-            if (ob) memset(ob, 0, sizeof(double) * C);
-            if (og) memset(og, 0, sizeof(double) * C * D);
+            real acc_b[C > 0 ? C : 1], acc_g[C > 0 ? C * D : 1]; /* sums of this particle */
+            real *ob = blur ? acc_b : NULL;
+            real *og = grad ? acc_g : NULL;
+            if (ob) memset(ob, 0, sizeof(real) * C);
+            if (og) memset(og, 0, sizeof(real) * C * D);
             FOR_EACH_CANDIDATE(&cl, c, xi, {
                 const float *xj = xb + (size_t)j * P;
-                double r[3] = {0, 0, 0};
-                const double q = pair_r(c, xi, xj, r);
+                real r[3] = {0, 0, 0};
+                const real q = pair_r(c, xi, xj, r);
                 if (count && pair_q_f32(c, xi, xj) < h2f) a_cnt += 1.0f;
-                const double mj = mb ? (double)mb[j] : 1.0;
-                const double vj = rb ? mj / (double)rb[j] : 0.0;
+                const real mj = mb ? RC(mb[j]) : RC(1.0);
+                const real vj = rb ? mj / RC(rb[j]) : RC(0.0);
                 if (q < h2) {
-                    double t = h2 - q;
-                    if (t < 0.0) t = 0.0;
-                    const double w = t * t * t;
+                    real t = h2 - q;
+                    if (t < RC(0.0)) t = RC(0.0);
+                    const real w = t * t * t;
                     a_rho += mj * w;
                     if (ob) {
                         const float *sj = sb + (size_t)j * C;
-                        for (int f = 0; f < C; ++f) ob[f] += (w * vj) * (double)sj[f];
+                        for (int f = 0; f < C; ++f) ob[f] += (w * vj) * RC(sj[f]);
                     }
                 }
-                double phi;
+                real phi;
                 if ((rho_grad || og || moment) && spiky(q, h, &phi, NULL)) {
                     for (int d = 0; d < D; ++d) a_dg[d] += mj * phi * r[d];
                     if (og) {
                         const float *sj = sb + (size_t)j * C;
                         const float *si = sb + (size_t)i * C;
                         for (int f = 0; f < C; ++f) {
-                            const double df = (double)sj[f] - (double)si[f];
+                            const real df = RC(sj[f]) - RC(si[f]);
                             for (int d = 0; d < D; ++d) og[f * D + d] += df * (vj * phi * r[d]);
                         }
                     }
@@ -298,9 +318,9 @@ int oracle_forward(const oracle_cfg *c, const float *x, const float *mass, const
             if (rho_grad)
                 for (int d = 0; d < D; ++d) rho_grad[gi * D + d] = cg * a_dg[d];
             if (ob)
-                for (int f = 0; f < C; ++f) ob[f] *= cs;
+                for (int f = 0; f < C; ++f) blur[gi * C + f] = cs * ob[f];
             if (og)
-                for (int f = 0; f < C * D; ++f) og[f] *= cg;
+                for (int f = 0; f < C * D; ++f) grad[gi * C * D + f] = cg * og[f];
             if (moment)
                 for (int p = 0; p < D * D; ++p) moment[gi * D * D + p] = cg * a_m[p];
         }
@@ -314,7 +334,7 @@ int oracle_forward(const oracle_cfg *c, const float *x, const float *mass, const
  * differentiates torch_sph.py (rho_in is an independent input of blur / gradient / moment_matrix).
  * Upstream gradients (float, any may be NULL = zero):
  *   g_rho [B,N], g_rho_grad [B,N,D], g_blur [B,N,C], g_grad [B,N,C,D], g_moment [B,N,D,D]
- * Outputs (double, any may be NULL): dx [B,N,D], ds [B,N,C], drho [B,N] (w.r.t. rho_in).
+ * Outputs (real, any may be NULL): dx [B,N,D], ds [B,N,C], drho [B,N] (w.r.t. rho_in).
  * With r = x_j - x_i, W = (h^2-q)^3, E = 6 (h^2-q)^2, K = phi r, J = phi I - psi r r^T,
  * v = m / rho_in:
  *   density      dx_i += cs sum_j E (g_i m_j + g_j m_i) r
@@ -333,8 +353,8 @@ int oracle_backward(const oracle_cfg *c, const float *x, const float *mass, cons
                     const float *g_blur, const float *g_grad, const float *g_moment, double *dx,
                     double *ds, double *drho) {
     const int N = c->particles, D = c->dim, C = c->channels, P = c->pos_stride;
-    const double h = c->h, h2 = h * h;
-    const double cs = poly6_norm(h, D), cg = spiky_norm(h, D);
+    const real h = RC(c->h), h2 = RC(c->h * c->h);
+    const real cs = poly6_norm(c->h, D), cg = spiky_norm(c->h, D);
     if ((g_blur || g_grad || g_moment) && !rho_in) return -1;
     if ((g_blur || g_grad) && (!s || C <= 0)) return -1;
     for (int b = 0; b < c->batch; ++b) {
@@ -353,43 +373,44 @@ int oracle_backward(const oracle_cfg *c, const float *x, const float *mass, cons
         for (int i = 0; i < N; ++i) {
             const float *xi = xb + (size_t)i * P;
             const size_t gi = (size_t)b * N + i;
-            const double mi = mb ? (double)mb[i] : 1.0;
-            const double vi = rb ? mi / (double)rb[i] : 0.0;
-            double a_dx[3] = {0, 0, 0}, a_dr = 0.0;
-            double *ods = ds ? ds + gi * C : NULL;
-            if (ods) memset(ods, 0, sizeof(double) * C);
+            const real mi = mb ? RC(mb[i]) : RC(1.0);
+            const real vi = rb ? mi / RC(rb[i]) : RC(0.0);
+            real a_dx[3] = {0, 0, 0}, a_dr = RC(0.0);
+            real acc_s[C > 0 ? C : 1];
+            real *ods = ds ? acc_s : NULL;
+            if (ods) memset(ods, 0, sizeof(real) * C);
             FOR_EACH_CANDIDATE(&cl, c, xi, {
                 const float *xj = xb + (size_t)j * P;
-                double r[3] = {0, 0, 0};
-                const double q = pair_r(c, xi, xj, r);
-                const double mj = mb ? (double)mb[j] : 1.0;
-                const double vj = rb ? mj / (double)rb[j] : 0.0;
+                real r[3] = {0, 0, 0};
+                const real q = pair_r(c, xi, xj, r);
+                const real mj = mb ? RC(mb[j]) : RC(1.0);
+                const real vj = rb ? mj / RC(rb[j]) : RC(0.0);
                 if (q < h2) {
-                    double t = h2 - q;
-                    if (t < 0.0) t = 0.0;
-                    const double W = t * t * t, E = 6.0 * t * t;
+                    real t = h2 - q;
+                    if (t < RC(0.0)) t = RC(0.0);
+                    const real W = t * t * t, E = RC(6.0) * t * t;
                     if (gr)
                         for (int d = 0; d < D; ++d)
-                            a_dx[d] += cs * E * ((double)gr[i] * mj + (double)gr[j] * mi) * r[d];
+                            a_dx[d] += cs * E * (RC(gr[i]) * mj + RC(gr[j]) * mi) * r[d];
                     if (gb) {
                         const float *sj = sb + (size_t)j * C, *si = sb + (size_t)i * C;
                         const float *gbj = gb + (size_t)j * C, *gbi = gb + (size_t)i * C;
-                        double A = 0.0, Bp = 0.0;
+                        real A = RC(0.0), Bp = RC(0.0);
                         for (int f = 0; f < C; ++f) {
-                            if (ods) ods[f] += cs * vi * W * (double)gbj[f];
-                            A += (double)gbi[f] * (double)sj[f];
-                            Bp += (double)gbj[f] * (double)si[f];
+                            if (ods) ods[f] += cs * vi * W * RC(gbj[f]);
+                            A += RC(gbi[f]) * RC(sj[f]);
+                            Bp += RC(gbj[f]) * RC(si[f]);
                         }
                         for (int d = 0; d < D; ++d) a_dx[d] += cs * E * r[d] * (vj * A + vi * Bp);
                         a_dr -= cs * (vi * vi / mi) * W * Bp;
                     }
                 }
-                double phi, psi;
+                real phi, psi;
                 if ((gd || gg || gm) && spiky(q, h, &phi, &psi)) {
                     if (gd) {
-                        double u[3] = {0, 0, 0}, ru = 0.0;
+                        real u[3] = {0, 0, 0}, ru = RC(0.0);
                         for (int d = 0; d < D; ++d) {
-                            u[d] = mi * (double)gd[(size_t)j * D + d] - mj * (double)gd[(size_t)i * D + d];
+                            u[d] = mi * RC(gd[(size_t)j * D + d]) - mj * RC(gd[(size_t)i * D + d]);
                             ru += r[d] * u[d];
                         }
                         for (int d = 0; d < D; ++d) a_dx[d] += cg * (phi * u[d] - psi * ru * r[d]);
@@ -397,15 +418,15 @@ int oracle_backward(const oracle_cfg *c, const float *x, const float *mass, cons
                     if (gg) {
                         const float *sj = sb + (size_t)j * C, *si = sb + (size_t)i * C;
                         const float *ggj = gg + (size_t)j * C * D, *ggi = gg + (size_t)i * C * D;
-                        double u[3] = {0, 0, 0}, ru = 0.0;
+                        real u[3] = {0, 0, 0}, ru = RC(0.0);
                         for (int f = 0; f < C; ++f) {
-                            const double df = (double)si[f] - (double)sj[f];
-                            double hk = 0.0, gk = 0.0;
+                            const real df = RC(si[f]) - RC(sj[f]);
+                            real hk = RC(0.0), gk = RC(0.0);
                             for (int d = 0; d < D; ++d) {
-                                const double hd = vj * (double)ggi[f * D + d] + vi * (double)ggj[f * D + d];
+                                const real hd = vj * RC(ggi[f * D + d]) + vi * RC(ggj[f * D + d]);
                                 hk += phi * r[d] * hd;
                                 u[d] += df * hd;
-                                gk += (double)ggj[f * D + d] * phi * r[d];
+                                gk += RC(ggj[f * D + d]) * phi * r[d];
                             }
                             if (ods) ods[f] -= cg * hk;
                             a_dr += cg * (vi * vi / mi) * df * gk;
@@ -415,14 +436,14 @@ int oracle_backward(const oracle_cfg *c, const float *x, const float *mass, cons
                     }
                     if (gm) {
                         const float *gmj = gm + (size_t)j * D * D, *gmi = gm + (size_t)i * D * D;
-                        double w[3] = {0, 0, 0}, rw = 0.0, rr = 0.0;
+                        real w[3] = {0, 0, 0}, rw = RC(0.0), rr = RC(0.0);
                         for (int p = 0; p < D; ++p) {
-                            double kc = 0.0;
+                            real kc = RC(0.0);
                             for (int e = 0; e < D; ++e) {
-                                const double cm = vj * (double)gmi[p * D + e] + vi * (double)gmj[p * D + e];
+                                const real cm = vj * RC(gmi[p * D + e]) + vi * RC(gmj[p * D + e]);
                                 kc += cm * phi * r[e];
                                 w[e] += r[p] * cm;
-                                rr += (double)gmj[p * D + e] * r[p] * r[e];
+                                rr += RC(gmj[p * D + e]) * r[p] * r[e];
                             }
                             a_dx[p] -= cg * kc;
                         }
@@ -435,6 +456,8 @@ int oracle_backward(const oracle_cfg *c, const float *x, const float *mass, cons
             if (dx)
                 for (int d = 0; d < D; ++d) dx[gi * D + d] = a_dx[d];
             if (drho) drho[gi] = a_dr;
+            if (ods)
+                for (int f = 0; f < C; ++f) ds[gi * C + f] = ods[f];
         }
         free_cells(&cl);
     }

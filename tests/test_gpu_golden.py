@@ -3,8 +3,8 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close, golden_names, load_golden
-from helpers import np64, tolerance
+from conftest import assert_parity, golden_names, load_golden
+from helpers import np64
 from npa_b200.workloads import Workload
 
 pytestmark = pytest.mark.gpu
@@ -43,7 +43,6 @@ def _unbin(t, perm):
 def test_forward_against_reference_outputs(name):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
-    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     if mass is None:
@@ -63,9 +62,7 @@ def test_forward_against_reference_outputs(name):
     np.testing.assert_array_equal(_unbin(got["count"], perm).cpu().numpy(), arr["f32_count"])
     for k in ("rho", "rho_grad", "blur", "grad", "moment"):
         out = np64(_unbin(got[k], perm))
-        assert_close(out, arr[f"f64_{k}"], RTOL, ATOL_SCALE, what=f"{name}:{k} vs fp64 reference")
-        # the reference's own fp32 run is itself only fp32-accurate: a looser cross-check
-        assert_close(out, arr[f"f32_{k}"], 1e-4, 4e-6, what=f"{name}:{k} vs fp32 reference")
+        assert_parity(out, arr[f"f64_{k}"], arr[f"f32_{k}"], what=f"{name}:{k} vs fp64 reference")
     # the fused forward gives the same tensors as the single operators
     rho_f, blur_f, grad_f, dg_f = sph.perceive(xb, sb, snap, mb)
     assert torch.equal(rho_f, got["rho"]) and torch.equal(dg_f, got["rho_grad"])
@@ -77,7 +74,6 @@ def test_forward_against_reference_outputs(name):
 def test_backward_against_reference_autograd(name):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
-    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     if mass is None:
@@ -106,13 +102,13 @@ def test_backward_against_reference_autograd(name):
     }
     for op, (fn, up) in ops.items():
         dx, ds, dr = run(fn, ups[up])
-        assert_close(np64(_unbin(dx, perm))[..., :dim], arr[f"f64_bw_{op}_dx"], RTOL, ATOL_SCALE, f"{name}:{op} dx")
+        assert_parity(np64(_unbin(dx, perm))[..., :dim], arr[f"f64_bw_{op}_dx"], arr[f"f32_bw_{op}_dx"], f"{name}:{op} dx")
         if dim == 3:
             assert float(dx[..., 3].abs().max()) == 0.0
         if f"f64_bw_{op}_ds" in arr:
-            assert_close(np64(_unbin(ds, perm)), arr[f"f64_bw_{op}_ds"], RTOL, ATOL_SCALE, f"{name}:{op} ds")
+            assert_parity(np64(_unbin(ds, perm)), arr[f"f64_bw_{op}_ds"], arr[f"f32_bw_{op}_ds"], f"{name}:{op} ds")
         if f"f64_bw_{op}_drho" in arr:
-            assert_close(np64(_unbin(dr, perm)), arr[f"f64_bw_{op}_drho"], RTOL, ATOL_SCALE, f"{name}:{op} drho")
+            assert_parity(np64(_unbin(dr, perm)), arr[f"f64_bw_{op}_drho"], arr[f"f32_bw_{op}_drho"], f"{name}:{op} drho")
 
 
 @pytest.mark.parametrize("name", golden_names())
@@ -120,7 +116,6 @@ def test_backward_against_reference_autograd(name):
 def test_chained_backward_against_reference_autograd(name, fused):
     sph, meta, arr, snap, perm, binned, x = _setup(name)
     dim, C = meta["dim"], meta["C"]
-    RTOL, ATOL_SCALE = tolerance(meta["periodic"])
     s = torch.from_numpy(arr["in_s"]).cuda()
     mass = torch.from_numpy(arr["in_mass"]).cuda() if "in_mass" in arr else None
     xr = x.clone().requires_grad_(True)
@@ -141,5 +136,5 @@ def test_chained_backward_against_reference_autograd(name, fused):
                             [binned("in_g_rho"), binned("in_g_blur", (C,)), binned("in_g_grad", (C, dim)),
                              binned("in_g_rho_grad", (dim,))])
     # gradients arrive in the original particle order through Permute.backward
-    assert_close(np64(xr.grad)[..., :dim], arr["f64_chain_dx"], RTOL, ATOL_SCALE, f"{name}: chain dx")
-    assert_close(np64(sr.grad), arr["f64_chain_ds"], RTOL, ATOL_SCALE, f"{name}: chain ds")
+    assert_parity(np64(xr.grad)[..., :dim], arr["f64_chain_dx"], arr["f32_chain_dx"], f"{name}: chain dx")
+    assert_parity(np64(sr.grad), arr["f64_chain_ds"], arr["f32_chain_ds"], f"{name}: chain ds")
