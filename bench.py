@@ -267,7 +267,7 @@ def run_gpu_arm(args, w):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB of L2
     phases = ["grid_build", "reorder", "density_sweep", "blur_gradient_sweep", "blur_gradient_backward",
               "density_backward"]
-    launches_per_step = 6 + 1 + 1 + 1 + 1 + 1
+    launches_per_step = 7 + 1 + 1 + 1 + 1 + 1  # grid build (7 kernels), reorder, four sweeps
 
     def step(ev=None):
         mark = (lambda k: ev[k].record()) if ev is not None else (lambda k: None)

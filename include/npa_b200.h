@@ -429,6 +429,40 @@ int npa_linear_tf32x3(const float *A, const float *W, const float *bias, const f
                       int64_t rows, int32_t in_dim, int32_t out_dim, int64_t w_stride_out,
                       int64_t w_stride_in, int32_t relu, void *stream);
 
+/*
+ * Cell-tile streaming engine of the blur + gradient sweeps (no counterpart in the reference's
+ * binding; the reference stages neighbour cells per block inside forward_kernel / backward_kernel,
+ * sphops/sph_cuda.cu:1561-1660, 903-1160, without a switch).
+ *
+ * When enabled, the fused blur + gradient sweeps (npa_blur_gradient_forward / _backward, the feature
+ * sweeps of npa_perception_* and npa_perceive_features_*) stage the rows of a tile's neighbour cells
+ * in shared memory with bulk asynchronous copies and read them from there.  The engine takes a call
+ * when the hash is linear, channels % 4 == 0 and <= 128, B * N % 4 == 0 and every tensor is 16-byte
+ * aligned; anything else runs on the gather kernels, with the same results to rounding.
+ *
+ * npa_tile_tuning: process-wide switches per direction (backward = 0 / 1): `enabled` = 0 (the
+ * default: on the measured workloads the gather kernels are as fast or faster) keeps the direction
+ * on the gather kernels; rows_per_stage (multiple of 4), particles_per_tile, stages
+ * (<= 4), consumer_warps (8 or 16 per CTA; 24 forward only) and cells_per_tile (work items of up
+ * to that many x-adjacent cells share one staged neighbourhood) size the plan, 0 = chosen
+ * automatically.  A plan that does not fit in shared memory falls back to the gather kernels.
+ *
+ * npa_tile_status: every wait inside the engine is bounded; a wait that runs out stores a code in a
+ * device word (1: a consumer gave up waiting for copies, 2: the producer gave up waiting for a free
+ * stage) and the launch drains without finishing its work.  This call copies the word to
+ * *host_status (0 = no wait ever ran out) and, with reset != 0, clears it.  It synchronises the
+ * device: call it outside the timed path, e.g. once after a step, never during stream capture.
+ */
+int npa_tile_tuning(int32_t backward, int32_t enabled, int32_t rows_per_stage,
+                    int32_t particles_per_tile, int32_t stages, int32_t consumer_warps,
+                    int32_t cells_per_tile);
+int npa_tile_status(int32_t *host_status, int32_t reset);
+/* Self-test of the bounded waits: one CTA waits for an mbarrier phase that is never completed and
+ * writes to *device_result (int32, device memory) 1 when the wait gave up after limit_us
+ * microseconds (the expected outcome) or 0 had it completed.  Faults nothing; the context stays
+ * usable. */
+int npa_tile_wait_selftest(int32_t limit_us, int32_t *device_result, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

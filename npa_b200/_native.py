@@ -86,6 +86,9 @@ SIGNATURES = {
     "npa_linear_tf32x3": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
                                          _I32, _P]),
     "npa_step_update_backward": (ctypes.c_int, [_P] * 3 + [_I32, ctypes.c_float, ctypes.c_float, _P, _P, _P, _P]),
+    "npa_tile_tuning": (ctypes.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
+    "npa_tile_status": (ctypes.c_int, [_P, _I32]),
+    "npa_tile_wait_selftest": (ctypes.c_int, [_I32, _P, _P]),
 }
 
 
@@ -120,6 +123,20 @@ def check(rc: int) -> None:
     if rc == NPA_ERR_UNSUPPORTED:
         raise ValueError(msg)
     raise RuntimeError(msg)
+
+
+def tile_tuning(backward: bool, enabled: bool = True, rows_per_stage: int = 0, particles_per_tile: int = 0,
+                stages: int = 0, consumer_warps: int = 0, cells_per_tile: int = 0) -> None:
+    """Process-wide switches of the cell-tile streaming engine (``npa_tile_tuning``)."""
+    check(lib.npa_tile_tuning(int(bool(backward)), int(bool(enabled)), int(rows_per_stage),
+                              int(particles_per_tile), int(stages), int(consumer_warps), int(cells_per_tile)))
+
+
+def tile_status(reset: bool = True) -> int:
+    """Status word of the engine's bounded waits (``npa_tile_status``); synchronises the device."""
+    out = ctypes.c_int32(0)
+    check(lib.npa_tile_status(ctypes.byref(out), int(bool(reset))))
+    return int(out.value)
 
 
 def make_grid(dim, boundary, mode, grid_size, eps, batch, particles, mpb) -> NpaGrid:

@@ -24,9 +24,15 @@ constexpr int kSmemHistCells = 8192;                   // 32 KB of shared histog
 constexpr int kScanThreads = 256;
 constexpr int kScanPerThread = 8;
 constexpr int kScanTile = kScanThreads * kScanPerThread;
+// Cells with more particles than this are ranked by rank_crowded_kernel (linear in the population)
+// instead of the per-particle scan of rank_kernel (quadratic in it).
+constexpr int kCrowdedCell = 256;
+constexpr int kRankWindow = 1 << 17;  // particle indices per bitmap window of rank_crowded_kernel (32 KB of shared memory)
+constexpr int kRankCtas = 64;
 
 struct BinScratch {
-    uint32_t *counts;   // [B*cells + 1]
+    uint32_t *counts;   // [B*cells + 1], then one word: number of crowded cells (zeroed with the counts)
+    uint32_t *crowded;  // [B*N / kCrowdedCell + 1] global cell index of each crowded cell
     uint32_t *arrive;   // [B*N]  arrival number of the particle inside its cell (any order)
     uint32_t *cellid;   // [B*N]
     uint32_t *order;    // [B*N]  slot -> particle, unsorted inside a cell
@@ -44,8 +50,10 @@ static size_t layout_scratch(const Geom &g, void *base, BinScratch *s) {
     size_t off = 0;
     char *p = (char *)base;
     size_t counts_off = off;
-    off += align_up((nc + 1) * 4);
+    off += align_up((nc + 2) * 4);
     size_t zero_end = off;
+    size_t crowded_off = off;
+    off += align_up((np / kCrowdedCell + 1) * 4);
     size_t arrive_off = off;
     off += align_up(np * 4);
     size_t cellid_off = off;
@@ -56,6 +64,7 @@ static size_t layout_scratch(const Geom &g, void *base, BinScratch *s) {
     off += align_up((size_t)(tiles + 1) * 8);
     if (s) {
         s->counts = (uint32_t *)(p + counts_off);
+        s->crowded = (uint32_t *)(p + crowded_off);
         s->arrive = (uint32_t *)(p + arrive_off);
         s->cellid = (uint32_t *)(p + cellid_off);
         s->order = (uint32_t *)(p + order_off);
@@ -219,7 +228,8 @@ scan_partials_kernel(unsigned long long *partials, int tiles) {
 // the unused tail of the work list (rows [total_items, max_blocks)).
 __global__ void __launch_bounds__(kScanThreads)
 scan_apply_kernel(const uint32_t *__restrict__ counts, const unsigned long long *__restrict__ partials,
-                  int32_t *__restrict__ bin_offsets, int4 *__restrict__ block_info, int n, Geom g) {
+                  int32_t *__restrict__ bin_offsets, int4 *__restrict__ block_info, uint32_t *__restrict__ crowded,
+                  uint32_t *__restrict__ crowded_count, int n, Geom g) {
     __shared__ unsigned long long tot;
     const int base = blockIdx.x * kScanTile + threadIdx.x * kScanPerThread;
     uint32_t c[kScanPerThread];
@@ -237,6 +247,7 @@ scan_apply_kernel(const uint32_t *__restrict__ counts, const unsigned long long 
             const uint32_t start = (uint32_t)run;
             uint32_t row = (uint32_t)(run >> 32);
             bin_offsets[cell] = (int32_t)start;
+            if (c[k] > (uint32_t)kCrowdedCell) crowded[atomicAdd(crowded_count, 1u)] = (uint32_t)cell;
             const int sys = cell / g.cells;
             for (uint32_t off = 0; off < c[k]; off += (uint32_t)g.mpb, ++row)
                 block_info[row] = make_int4(cell, (int)off, (int)min((uint32_t)g.mpb, c[k] - off), sys);
@@ -277,9 +288,74 @@ rank_kernel(const uint32_t *__restrict__ cellid, const int32_t *__restrict__ bin
     const uint32_t key = cellid[sys + i];
     const size_t cell = (size_t)b * g.cells + key;
     const uint32_t s = (uint32_t)bin_offsets[cell], e = (uint32_t)bin_offsets[cell + 1];
+    if (e - s > (uint32_t)kCrowdedCell) return;  // ranked by rank_crowded_kernel
     uint32_t rank = 0;
     for (uint32_t q = s; q < e; ++q) rank += order[q] < i ? 1u : 0u;
     permutation[sys + i] = (int32_t)(s - (uint32_t)sys + rank);
+}
+
+// Stable ranks inside crowded cells (a collapsed system, or particles clamped into an edge cell): a
+// CTA takes one crowded cell at a time, marks the original indices of its particles in a bitmap over
+// the system's particle indices (in windows of kRankWindow indices), turns the bitmap into prefix
+// popcounts, and a particle's rank is the number of marked indices below its own.  Linear in the
+// population plus N / 32 words per window; no sort, no atomics in global memory.
+__global__ void __launch_bounds__(256)
+rank_crowded_kernel(const int32_t *__restrict__ bin_offsets, const uint32_t *__restrict__ order,
+                    int32_t *__restrict__ permutation, const uint32_t *__restrict__ crowded,
+                    const uint32_t *__restrict__ crowded_count, Geom g) {
+    extern __shared__ uint32_t rank_smem[];
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t carry;
+    const int win = g.N < kRankWindow ? g.N : kRankWindow;
+    const int words = (win + 31) / 32;
+    uint32_t *bits = rank_smem, *pre = rank_smem + words;
+    const uint32_t n = *crowded_count;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (uint32_t entry = blockIdx.x; entry < n; entry += gridDim.x) {
+        const uint32_t cell = crowded[entry];
+        const uint32_t sys = (cell / (uint32_t)g.cells) * (uint32_t)g.N;
+        const uint32_t s = (uint32_t)bin_offsets[cell], e = (uint32_t)bin_offsets[cell + 1];
+        uint32_t below = 0;  // particles of the cell with an index below the current window
+        for (uint32_t w0 = 0; w0 < (uint32_t)g.N; w0 += (uint32_t)win) {
+            for (int k = threadIdx.x; k < words; k += 256) bits[k] = 0u;
+            if (threadIdx.x == 0) carry = 0u;
+            __syncthreads();
+            for (uint32_t q = s + threadIdx.x; q < e; q += 256) {
+                const uint32_t i = order[q] - w0;
+                if (i < (uint32_t)win) atomicOr(&bits[i >> 5], 1u << (i & 31));
+            }
+            __syncthreads();
+            // exclusive prefix of the word popcounts, 256 words per round
+            for (int base = 0; base < words; base += 256) {
+                const int k = base + threadIdx.x;
+                const uint32_t v = k < words ? (uint32_t)__popc(bits[k]) : 0u;
+                uint32_t inc = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t t = __shfl_up_sync(kFull, inc, o);
+                    if (lane >= o) inc += t;
+                }
+                if (lane == 31) warp_tot[w] = inc;
+                __syncthreads();
+                uint32_t before = carry;
+                for (int ww = 0; ww < w; ++ww) before += warp_tot[ww];
+                if (k < words) pre[k] = before + inc - v;
+                __syncthreads();
+                if (threadIdx.x == 255) carry = before + inc;
+                __syncthreads();
+            }
+            for (uint32_t q = s + threadIdx.x; q < e; q += 256) {
+                const uint32_t idx = order[q];
+                const uint32_t i = idx - w0;
+                if (i < (uint32_t)win) {
+                    const uint32_t rank = below + pre[i >> 5] + (uint32_t)__popc(bits[i >> 5] & ((1u << (i & 31)) - 1u));
+                    permutation[sys + idx] = (int32_t)(s - sys + rank);
+                }
+            }
+            below += carry;
+            __syncthreads();
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -425,15 +501,20 @@ int npa_grid_build(const npa_grid *gd, const float *x, int32_t *permutation, int
     if ((rc = check_launch("scan_tile_sums_kernel")) != NPA_OK) return rc;
     scan_partials_kernel<<<1, 1024, 0, st>>>(s.partials, s.tiles);
     if ((rc = check_launch("scan_partials_kernel")) != NPA_OK) return rc;
+    uint32_t *crowded_count = s.counts + (size_t)n + 1;
     scan_apply_kernel<<<s.tiles, kScanThreads, 0, st>>>(s.counts, s.partials, bin_offsets,
-                                                        reinterpret_cast<int4 *>(block_info), n, g);
+                                                        reinterpret_cast<int4 *>(block_info), s.crowded, crowded_count, n, g);
     if ((rc = check_launch("scan_apply_kernel")) != NPA_OK) return rc;
 
     const dim3 tgrid((g.N + kBinThreads - 1) / kBinThreads, g.B);
     scatter_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, s.arrive, bin_offsets, s.order, g);
     if ((rc = check_launch("scatter_kernel")) != NPA_OK) return rc;
     rank_kernel<<<tgrid, kBinThreads, 0, st>>>(s.cellid, bin_offsets, s.order, permutation, g);
-    return check_launch("rank_kernel");
+    if ((rc = check_launch("rank_kernel")) != NPA_OK) return rc;
+    const int win = g.N < kRankWindow ? g.N : kRankWindow;
+    rank_crowded_kernel<<<kRankCtas, 256, (size_t)((win + 31) / 32) * 8, st>>>(bin_offsets, s.order, permutation, s.crowded,
+                                                                             crowded_count, g);
+    return check_launch("rank_crowded_kernel");
 }
 
 }  // extern "C"

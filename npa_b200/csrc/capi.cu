@@ -4,6 +4,7 @@
 // perception calls.
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <utility>
 
 #include "ops.cuh"
@@ -34,18 +35,22 @@ int launch_feature_backward(const Geom &g, int mask, bool full, const FeatureBwd
 
 int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *out) {
     static std::mutex mu;
-    static std::map<std::pair<int, const void *>, int> cache;
+    static std::map<std::tuple<int, const void *, int, size_t>, int> cache;
+    static std::map<std::pair<int, const void *>, size_t> smem_limit;  // largest dynamic size enabled so far
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
     std::lock_guard<std::mutex> lock(mu);
-    auto key = std::make_pair(dev, kernel);
+    auto key = std::make_tuple(dev, kernel, threads, dyn_smem);
     auto it = cache.find(key);
     if (it == cache.end()) {
         int sms = 0, per_sm = 0;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e == cudaSuccess && dyn_smem > 0)
+        size_t &enabled = smem_limit[std::make_pair(dev, kernel)];
+        if (e == cudaSuccess && dyn_smem > enabled) {
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
+            if (e == cudaSuccess) enabled = dyn_smem;
+        }
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem);
         if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "sizing a persistent launch: %s", cudaGetErrorString(e));
         it = cache.emplace(key, sms * (per_sm > 0 ? per_sm : 1)).first;

@@ -669,6 +669,11 @@ int launch_feature_forward_shape(const Geom &g, int mask, const FeatureFwdArgs &
 
 template <int D, bool PER>
 int launch_feature_forward_geom(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st) {
+    {
+        bool taken = false;  // the cell-tile streaming engine takes the shapes it covers
+        const int rc = launch_feature_tile_forward<D, PER>(g, mask, a, st, &taken);
+        if (rc != NPA_OK || taken) return rc;
+    }
     if (feature_rows_vectorisable(a.C, a.s, a.blur, a.grad, nullptr, nullptr)) {
         const int need = a.C / 4;
         if (need <= 4) return launch_feature_forward_shape<D, PER, 4, 4>(g, mask, a, st);
@@ -710,6 +715,11 @@ int launch_feature_backward_shape(const Geom &g, int mask, const FeatureBwdArgs 
 
 template <int D, bool PER, bool FULL>
 int launch_feature_backward_geom(const Geom &g, int mask, const FeatureBwdArgs &a, cudaStream_t st) {
+    {
+        bool taken = false;  // the cell-tile streaming engine takes the shapes it covers
+        const int rc = launch_feature_tile_backward<D, PER, FULL>(g, mask, a, st, &taken);
+        if (rc != NPA_OK || taken) return rc;
+    }
     if (feature_rows_vectorisable(a.C, a.s, a.g_blur, a.g_grad, a.grad_s, nullptr)) {
         const int need = a.C / 4;
         if (need <= 4) return launch_feature_backward_shape<D, PER, 4, 4, FULL>(g, mask, a, st);

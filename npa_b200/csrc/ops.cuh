@@ -107,6 +107,13 @@ int persistent_ctas(Kernel kernel, int threads, size_t dyn_smem, int *out) {
 // Defined in capi.cu.
 int acquire_row_tickets(cudaStream_t st, unsigned int **out);
 
+// The same sweeps on the cell-tile streaming engine (feature_tile.cuh).  *taken = false means the
+// engine does not cover this call (nothing was launched) and the gather kernel must run.
+template <int D, bool PER>
+int launch_feature_tile_forward(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st, bool *taken);
+template <int D, bool PER, bool FULL>
+int launch_feature_tile_backward(const Geom &g, int mask, const FeatureBwdArgs &a, cudaStream_t st, bool *taken);
+
 int launch_scalar_forward(const Geom &g, int mask, const ScalarFwdArgs &a, cudaStream_t st);
 int launch_scalar_backward(const Geom &g, int mask, const ScalarBwdArgs &a, cudaStream_t st);
 int launch_feature_forward(const Geom &g, int mask, const FeatureFwdArgs &a, cudaStream_t st);

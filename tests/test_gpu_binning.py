@@ -51,6 +51,33 @@ def test_binning_all_in_one_cell_and_empty_cells():
     assert torch.equal(snap.permutation.cpu(), torch.arange(w.N, dtype=torch.int32).expand(w.B, -1))
 
 
+@pytest.mark.parametrize("N", [65536, 300000])
+def test_binning_collapsed_system_is_ranked_in_linear_time(N):
+    """Every particle of a large system in one cell (a diverged rollout, or particles clamped into an
+    edge cell), next to a system with a few crowded cells: bit-exact and stable, and the grid build
+    stays far from the quadratic per-cell scan (which needs N^2 / 2 comparisons: seconds at this size)."""
+    import time
+    from npa_b200 import sphops as sph
+    w = Workload("collapsed", dim=3, B=2, N=N, C=4, eps=0.1, grid_size=(12, 12, 12), max_particles_per_block=64)
+    g = torch.Generator().manual_seed(2)
+    x = torch.zeros(w.B, w.N, 4)
+    x[0, :, :3] = 0.031 + 0.01 * torch.rand(w.N, 3, generator=g)            # one cell holds the whole system
+    x[1, :, :3] = (torch.rand(w.N, 3, generator=g) - 0.5) * 1.1
+    x[1, : w.N // 2, :3] = x[1, : w.N // 2, :3] * 0.05                        # half the system in a handful of cells
+    snap = _check(sph, w, x)
+    assert torch.equal(snap.permutation[0].cpu(), torch.arange(w.N, dtype=torch.int32))
+    grid = make_grid(sph, w)
+    xc = x.cuda()
+    grid.instantiate(xc)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        grid.instantiate(xc)
+    torch.cuda.synchronize()
+    per_build = (time.perf_counter() - t0) / 5
+    assert per_build < 5e-3, f"grid build of a collapsed system took {per_build * 1e3:.2f} ms"
+
+
 def test_binning_is_deterministic_and_reusable():
     from npa_b200 import sphops as sph
     w = scaled(CONFIGS["cfg2_2d_texture_blobs"], B=2, N=8192)
