@@ -63,7 +63,7 @@ def _grid(c):
 
 def _close(a, b, what, rtol=1e-5, atol=1e-6):
     """Two fp32 evaluations of the same formulas (operator by operator with torch glue, and fused):
-    each within rounding of the other, 1e-5 relative / 1e-6 of the tensor's scale."""
+    held to the stated bar, 1e-5 relative / 1e-6 of the tensor's scale, elementwise."""
     a, b = a.detach().double(), b.detach().double()
     scale = float(b.abs().max())
     err = (a - b).abs()
@@ -96,7 +96,7 @@ def test_perceive_of_the_reference_model(ref_npa, case, stopgrad_pos):
     if stopgrad_pos:
         assert xr.grad is None or float(xr.grad.abs().max()) == 0.0
     else:
-        _close(xf.grad, xr.grad, f"{case}: dL/dx", rtol=1e-4, atol=2e-5)
+        _close(xf.grad, xr.grad, f"{case}: dL/dx")
 
 
 @pytest.mark.parametrize("case", sorted(CASES))
@@ -133,7 +133,7 @@ def test_two_euler_steps_of_the_reference_model(ref_npa, case, stopgrad_pos):
     x_new, s_new, ds_new, g_new = rollout(stepping.step_euler)
     _close(x_new, x_ref, f"{case}: positions after two steps")
     _close(s_new, s_ref, f"{case}: states after two steps")
-    _close(ds_new, ds_ref, f"{case}: dL/ds0", rtol=1e-4, atol=1e-5)
+    _close(ds_new, ds_ref, f"{case}: dL/ds0")
     assert set(g_new) == set(g_ref) and g_ref
     for name in g_ref:
-        _close(g_new[name], g_ref[name], f"{case}: grad of {name}", rtol=1e-4, atol=1e-5)
+        _close(g_new[name], g_ref[name], f"{case}: grad of {name}")
