@@ -16,11 +16,17 @@
  *    the thread-local text returned by npa_last_error(), per-device launch
  *    sizes, and a small device array of row-ticket counters that its sweep
  *    kernels draw work from (two words per launch, zero again when the launch
- *    ends).  The first call of an operator on a device queries those once:
+ *    ends).  Slots are handed out round robin, 4096 for eager launches: sweeps
+ *    issued on different streams must lie fewer than 4096 launches apart to be
+ *    sure of distinct words.  Launches recorded under stream capture draw from
+ *    4096 further slots that are never reused (the graph owns them); the 4097th
+ *    captured sweep of a process is refused with NPA_ERR_UNSUPPORTED.  The first call of an operator on a device queries those once:
  *    make it before any stream capture.
  *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
- *  - Return value: NPA_OK (0) or a negative npa_status; on error nothing has
- *    been launched.  No C++ exception crosses this boundary.
+ *  - Return value: NPA_OK (0) or a negative npa_status.  Arguments are checked
+ *    before the first kernel of a call is enqueued, so an argument error means
+ *    nothing has been launched; only a failing kernel launch (NPA_ERR_CUDA) can
+ *    interrupt a multi-kernel call midway.  No C++ exception crosses this boundary.
  *  - `mass` may be NULL: every particle then has mass 1.0
  *    (sphops/sph.py:11-14, sph_cuda.cu:1843).
  */
@@ -457,6 +463,21 @@ int npa_tile_tuning(int32_t backward, int32_t enabled, int32_t rows_per_stage,
                     int32_t particles_per_tile, int32_t stages, int32_t consumer_warps,
                     int32_t cells_per_tile);
 int npa_tile_status(int32_t *host_status, int32_t reset);
+/* Health check of the row-ticket words the sweep kernels draw work from (no counterpart in the
+ * reference).  Every sweep leaves its two words zero; with no sweep in flight a non-zero word means a
+ * launch was cut short (a sticky CUDA error, a killed context) and later sweeps that draw the same
+ * slot would skip rows.  Writes the number of non-zero words to *host_nonzero_words and, with reset
+ * != 0, clears them.  Synchronises the device: call it after an error status, never in the timed path
+ * or during stream capture. */
+int npa_row_tickets_status(int32_t *host_nonzero_words, int32_t reset);
+/* The forward sweeps of the scalar operators (count, density, density gradient, moment matrix) on a
+ * linear-hash grid let the particles of a tile -- work items of up to cells_per_tile x-adjacent
+ * cells, at most 32 particles -- share the candidates they test (the sharing of a staged cell among
+ * the threads of a block in sphops/sph_cuda.cu:1664-1690).  Used for the poly6 operators (count,
+ * density) on clamped grids and 2D periodic grids, where it is measured faster; adding 100 forces it
+ * on 3D periodic grids too.  cells_per_tile = 0 switches back to the per-particle candidate walk;
+ * default 3.  Process-wide. */
+int npa_scalar_sweep_tuning(int32_t cells_per_tile);
 /* Self-test of the bounded waits: one CTA waits for an mbarrier phase that is never completed and
  * writes to *device_result (int32, device memory) 1 when the wait gave up after limit_us
  * microseconds (the expected outcome) or 0 had it completed.  Faults nothing; the context stays

@@ -88,6 +88,8 @@ SIGNATURES = {
     "npa_step_update_backward": (ctypes.c_int, [_P] * 3 + [_I32, ctypes.c_float, ctypes.c_float, _P, _P, _P, _P]),
     "npa_tile_tuning": (ctypes.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
     "npa_tile_status": (ctypes.c_int, [_P, _I32]),
+    "npa_scalar_sweep_tuning": (ctypes.c_int, [_I32]),
+    "npa_row_tickets_status": (ctypes.c_int, [_P, _I32]),
     "npa_tile_wait_selftest": (ctypes.c_int, [_I32, _P, _P]),
 }
 
@@ -136,6 +138,13 @@ def tile_status(reset: bool = True) -> int:
     """Status word of the engine's bounded waits (``npa_tile_status``); synchronises the device."""
     out = ctypes.c_int32(0)
     check(lib.npa_tile_status(ctypes.byref(out), int(bool(reset))))
+    return int(out.value)
+
+
+def row_tickets_nonzero(reset: bool = False) -> int:
+    """Number of non-zero row-ticket words (``npa_row_tickets_status``); 0 when every sweep ended cleanly."""
+    out = ctypes.c_int32(0)
+    check(lib.npa_row_tickets_status(ctypes.byref(out), int(bool(reset))))
     return int(out.value)
 
 

@@ -59,7 +59,7 @@ int persistent_ctas_impl(const void *kernel, int threads, size_t dyn_smem, int *
     return NPA_OK;
 }
 
-constexpr int kTicketSlots = 1024;  // first half: eager launches; second half: launches under stream capture
+constexpr int kTicketSlots = 8192;  // first half: eager launches; second half: launches under stream capture
 static __device__ unsigned int g_row_tickets[kTicketSlots * 2];  // zero at load; every launch leaves its words zero
 
 int acquire_row_tickets(cudaStream_t st, unsigned int **out) {
@@ -82,8 +82,31 @@ int acquire_row_tickets(cudaStream_t st, unsigned int **out) {
         if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "cudaGetSymbolAddress(row tickets): %s", cudaGetErrorString(e));
         base[dev] = static_cast<unsigned int *>(p);
     }
+    if (half == 1 && next[1] >= (unsigned)(kTicketSlots / 2))
+        // a replaying graph owns its words for as long as it exists: never hand one out twice
+        return fail(NPA_ERR_UNSUPPORTED, "more than %d sweeps have been recorded under stream capture in this process",
+                    kTicketSlots / 2);
     const unsigned int slot = half * (kTicketSlots / 2) + next[half]++ % (kTicketSlots / 2);
     *out = base[dev] + 2 * slot;
+    return NPA_OK;
+}
+
+// Host-side check of the ticket words (synchronises): every sweep leaves its two words zero, so a
+// non-zero word with no sweep in flight means a launch was cut short (e.g. a sticky CUDA error) and
+// later sweeps drawing that slot would skip rows.
+static int row_tickets_status(int *nonzero, bool reset) {
+    static unsigned int host[kTicketSlots * 2];
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_row_tickets, sizeof(host));
+    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "row_tickets_status: %s", cudaGetErrorString(e));
+    int n = 0;
+    for (unsigned int v : host) n += v != 0u;
+    *nonzero = n;
+    if (reset && n) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_row_tickets);
+        if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(host));
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "row_tickets_status: %s", cudaGetErrorString(e));
+    }
     return NPA_OK;
 }
 
@@ -345,6 +368,13 @@ int npa_perception_forward(const npa_grid *gd, int32_t channels, const float *x_
     cudaStream_t st = (cudaStream_t)stream;
     int smask = S_DENSITY | (count ? S_COUNT : 0) | (rho_grad ? S_DGRAD : 0);
     if ((rc = check_pair_cache("perception_forward", pair_cache, pair_stride)) != NPA_OK) return rc;
+    // every argument is checked before the first sweep is enqueued
+    if (s_blur || s_grad) {
+        if ((rc = check_channels("perception_forward", channels)) != NPA_OK) return rc;
+        NPA_REQUIRE(s_bin, "perception_forward", "state_in");
+    }
+    if (moment && g.dim == 2 && (uintptr_t)moment % 16)
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perception_forward: moment must be 16-byte aligned");
     ScalarFwdArgs sa = {x_bin, mass, nullptr, count, rho, rho_grad, nullptr, bin_offsets, block_info, pair_cache, pair_stride};
     if ((rc = launch_scalar_forward(g, smask, sa, st)) != NPA_OK) return rc;
     const int fmask = (s_blur ? F_BLUR : 0) | (s_grad ? F_GRAD : 0);
@@ -413,6 +443,14 @@ int npa_perception_backward(const npa_grid *gd, int32_t channels, const float *x
         }
     }
     return NPA_OK;
+}
+
+int npa_row_tickets_status(int32_t *host_nonzero_words, int32_t reset) {
+    if (!host_nonzero_words) return fail(NPA_ERR_INVALID_ARGUMENT, "row_tickets_status: host_nonzero_words is NULL");
+    int n = 0;
+    const int rc = row_tickets_status(&n, reset != 0);
+    if (rc == NPA_OK) *host_nonzero_words = n;
+    return rc;
 }
 
 }  // extern "C"

@@ -177,6 +177,48 @@ __device__ inline int build_ranges(const Geom &g, const int32_t *__restrict__ bi
     return __popc(m);
 }
 
+// Candidate ranges of a tile that covers the cells [cx0, cx1] of one x-row (cy, cz) of system `sys`:
+// per neighbour row (3 in 2D, 9 in 3D) the cells [cx0 - 1, cx1 + 1], which are contiguous in cell
+// order, plus on a periodic grid the wrapped cell beyond either end with its image shift.  The caller
+// guarantees cx1 - cx0 + 3 < g.g[0] unless the window is the whole row (then one range per row with
+// no shift; displacement() falls back to the general minimum image per pair).  Fills rng[0..n) with
+// (start, end, shift code, 0) of the non-empty ranges and returns n.  All 32 lanes call it.
+template <int D>
+__device__ inline int build_ranges_span(const Geom &g, const int32_t *__restrict__ bin_offsets, int sys, int cx0,
+                                        int cx1, int cy, int cz, int4 *rng) {
+    const int lane = threadIdx.x & 31;
+    const int32_t *off = bin_offsets + (size_t)sys * g.cells;
+    int start = 0, end = 0, sx = 0, sy = 0, sz = 0;
+    const int row = lane / 3, piece = lane % 3;  // piece 0: main window, 1: wrapped below, 2: wrapped above
+    if (row < (D == 2 ? 3 : 9)) {
+        int ny = 0, nz = 0;
+        bool ok = neighbor_axis(cy, row % 3 - 1, g.g[1], g.periodic, ny, sy);
+        if (D == 3) ok = neighbor_axis(cz, row / 3 - 1, g.g[2], g.periodic, nz, sz) && ok;
+        const int gx = g.g[0];
+        int xlo = 0, xhi = -1;
+        if (!g.periodic) {
+            if (piece == 0) { xlo = max(cx0 - 1, 0); xhi = min(cx1 + 1, gx - 1); }
+        } else if (cx1 - cx0 + 3 >= gx) {
+            if (piece == 0) { xlo = 0; xhi = gx - 1; }
+        } else if (piece == 0) {
+            xlo = max(cx0 - 1, 0); xhi = min(cx1 + 1, gx - 1);
+        } else if (piece == 1) {
+            if (cx0 == 0) { xlo = xhi = gx - 1; sx = -1; }
+        } else {
+            if (cx1 == gx - 1) { xlo = xhi = 0; sx = 1; }
+        }
+        if (ok && xhi >= xlo) {
+            start = __ldg(off + cell_hash<D>(g, xlo, ny, nz));
+            end = __ldg(off + cell_hash<D>(g, xhi, ny, nz) + 1);
+        }
+    }
+    const bool nonempty = end > start;
+    const unsigned m = __ballot_sync(kFull, nonempty);
+    if (nonempty) rng[__popc(m & ((1u << lane) - 1))] = make_int4(start, end, shift_code(sx, sy, sz), 0);
+    __syncwarp();
+    return __popc(m);
+}
+
 template <int D>
 struct Pos {
     float x, y, z;

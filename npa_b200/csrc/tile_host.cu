@@ -6,6 +6,8 @@
 
 namespace npa {
 
+void set_scalar_shared_span(int span);  // scalar_ops.cu
+
 static int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // Largest dynamic shared memory a CTA may ask for on this architecture (227 KB on sm_100) minus
@@ -119,6 +121,13 @@ int npa_tile_tuning(int32_t backward, int32_t enabled, int32_t rows_per_stage, i
                     kTileBatch);
     g_tuning[backward ? 1 : 0] = TileTuning{rows_per_stage, particles_per_tile, stages, enabled ? 1 : 0,
                                             consumer_warps ? consumer_warps : kTileWarpsDefault, cells_per_tile};
+    return NPA_OK;
+}
+
+int npa_scalar_sweep_tuning(int32_t cells_per_tile) {
+    if (cells_per_tile < 0 || (cells_per_tile > 8 && (cells_per_tile < 101 || cells_per_tile > 108)))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "scalar_sweep_tuning: cells_per_tile must be in [0, 8] (+100: also on 3D periodic grids)");
+    set_scalar_shared_span(cells_per_tile);
     return NPA_OK;
 }
 

@@ -17,6 +17,7 @@ inputs that do not require grad are returned as ``None``.
 from __future__ import annotations
 
 import math
+import weakref
 from dataclasses import dataclass, field
 
 import torch
@@ -88,6 +89,7 @@ class HashGrid:
         self.hashgrid_cls = get_hashgrid_cls(dim, boundary, mode)
         self.hashgrid = self.hashgrid_cls(*grid_size, eps, num_particles, batch_size, max_particles_per_block)
         self.device = torch.device("cuda") if device is None else torch.device(device)
+        self._last_snapshot = None
 
     def instantiate(self, x):
         """Bin positions ``x [B, N, P]`` and return the snapshot the operators take."""
@@ -97,8 +99,15 @@ class HashGrid:
         bin_offsets = torch.empty(B * self.num_cells + 1, dtype=torch.int32, device=dev)
         block_info = torch.empty(self.hashgrid.max_blocks, 4, dtype=torch.int32, device=dev)
         self.hashgrid.initialize(x, permutation, bin_offsets, block_info)
-        return HashGridSnapshot(grid=self.hashgrid, bin_offsets=bin_offsets, permutation=permutation,
-                                block_info=block_info, dim=self.dim)
+        # outputs a fused sweep parked on the previous snapshot and nobody claimed are dropped now: they would
+        # otherwise live (with the autograd graph they hang on) for as long as that snapshot does
+        previous = self._last_snapshot() if self._last_snapshot is not None else None
+        if previous is not None:
+            previous.parked.clear()
+        snapshot = HashGridSnapshot(grid=self.hashgrid, bin_offsets=bin_offsets, permutation=permutation,
+                                    block_info=block_info, dim=self.dim)
+        self._last_snapshot = weakref.ref(snapshot)
+        return snapshot
 
     def wrap_positions(self, x):
         """Periodic: map each of the ``dim`` coordinates into ``[-L/2, L/2)``; clamped: identity."""
@@ -156,13 +165,15 @@ def fusion_enabled():
 
 
 def _key(*tensors):
-    """Identity + version of the input tensor objects (None allowed); the objects are kept alive."""
-    return tuple((t, None if t is None else t._version) for t in tensors)
+    """Identity + version of the input tensor objects (None allowed), held weakly: a parked output never
+    keeps its inputs alive, and an input that has died can never match again."""
+    return tuple((None if t is None else weakref.ref(t), None if t is None else t._version) for t in tensors)
 
 
 def _same(key, *tensors):
     return len(key) == len(tensors) and all(
-        (kt is t) and (t is None or kv == t._version) for (kt, kv), t in zip(key, tensors))
+        (t is None and kt is None) or (t is not None and kt is not None and kt() is t and kv == t._version)
+        for (kt, kv), t in zip(key, tensors))
 
 
 def _park(snapshot, name, key, value):

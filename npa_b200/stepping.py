@@ -25,6 +25,22 @@ def _scalar(v) -> float:
     return float(v.item()) if isinstance(v, torch.Tensor) else float(v)
 
 
+def _buffer_scalar(model, name) -> float:
+    """``model.<name>`` (a one-element buffer such as ``eps0`` or ``alpha``) as a Python float, read from
+    the device once and cached on the module until the buffer is modified in place or replaced: a step
+    then makes no device-to-host copy (the reference keeps these as device tensors and never syncs)."""
+    v = getattr(model, name)
+    if not isinstance(v, torch.Tensor):
+        return float(v)
+    cache = model.__dict__.setdefault("_npa_b200_scalars", {})
+    hit = cache.get(name)
+    if hit is not None and hit[0] is v and hit[1] == v._version:
+        return hit[2]
+    value = float(v.item())
+    cache[name] = (v, v._version, value)
+    return value
+
+
 class _FrozenView:
     """The attributes of an NPA module that a step reads, with ``eps0`` and ``alpha`` as Python floats."""
 
@@ -55,7 +71,7 @@ def perceive(model, x, s, grid):
     x_bin, s_bin = sph.bin_particles(x, s, snapshot)
     x_perceive = x_bin.detach() if getattr(model, "stopgrad_pos", True) else x_bin
     s_perceive = s_bin.detach() if getattr(model, "stopgrad_state", False) else s_bin
-    z = sph.perceive_features(x_perceive, s_perceive, snapshot, _scalar(model.eps0),
+    z = sph.perceive_features(x_perceive, s_perceive, snapshot, _buffer_scalar(model, "eps0"),
                               log_norm_grad=getattr(model, "log_norm_grad", True),
                               log_norm_density_grad=getattr(model, "log_norm_density_grad", True))
     return z, x_bin, s_bin, snapshot
@@ -75,13 +91,13 @@ def step_euler(model, x, s, grid, dt=1.0, update_prob=0.5, intermediate=False, n
     stats = None
     if intermediate:
         d = y[..., : model.spatial_dims]
-        dx = _scalar(model.alpha) * d * grid.eps / (1.0 + d.norm(dim=-1, keepdim=True))
+        dx = _buffer_scalar(model, "alpha") * d * grid.eps / (1.0 + d.norm(dim=-1, keepdim=True))
         stats = {"dx_norm": dx.norm(dim=-1).mean()}
 
     update_mask = None
     if update_prob < 1.0:
         update_mask = (torch.rand(B, N, 1, device=x.device) < update_prob).float()
-    x_new, s_new = sph.step_update(y, x_bin, s_bin, snapshot, _scalar(model.alpha), dt, update_mask, wrap)
+    x_new, s_new = sph.step_update(y, x_bin, s_bin, snapshot, _buffer_scalar(model, "alpha"), dt, update_mask, wrap)
     if noise_std > 0:
         noise = torch.randn_like(x_new) * noise_std * math.sqrt(dt)
         x_new = x_new + (noise * update_mask if update_mask is not None else noise)

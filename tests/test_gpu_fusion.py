@@ -181,3 +181,36 @@ def test_packed_perception_equals_the_operator_sequence(dim, boundary, C, stopgr
         assert torch.allclose(gxp, gxr, rtol=1e-4, atol=2e-5 * float(gxr.abs().max()))
     with torch.no_grad():                   # inference path keeps no tensor for backward
         assert torch.equal(packed(x.cuda(), s.cuda()), zp)
+
+
+def test_unclaimed_parked_outputs_do_not_accumulate(fusion):
+    """A caller that uses only density + blur never claims the parked gradient / moment matrix / density
+    gradient.  They are dropped at the next instantiate(), and the weakly held input keys keep nothing alive:
+    device memory stays flat over many steps, also while older snapshots are kept (a BPTT rollout)."""
+    sph = fusion
+    w = Workload("park", dim=3, B=2, N=4000, C=16, eps=0.12, grid_size=(10, 10, 10))
+    x, s, _ = make_inputs(w, seed=9)
+    x, s = x.cuda(), s.cuda()
+    grid = make_grid(sph, w)
+    kept = []
+
+    def step():
+        snap = grid.instantiate(x)
+        xb, sb = sph.bin_particles(x, s, snap)
+        rho = sph.density(xb, snap)
+        out = sph.blur(xb, rho, sb, snap)
+        kept.append(snap)          # snapshots of every step stay alive, their parked outputs must not
+        return float(out.sum())
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    snapshots_only = sum(t.numel() * t.element_size() for sn in kept[-1:] for t in (sn.bin_offsets, sn.permutation, sn.block_info))
+    base = torch.cuda.memory_allocated()
+    for _ in range(10):
+        step()
+    torch.cuda.synchronize()
+    grown = torch.cuda.memory_allocated() - base
+    # ten more snapshots (offsets, permutation, work list) and nothing else
+    assert grown <= 10 * snapshots_only + (1 << 20), f"device memory grew by {grown} bytes over ten steps"
+    assert all(not sn.parked for sn in kept[:-1])

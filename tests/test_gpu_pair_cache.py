@@ -131,3 +131,27 @@ def test_public_api_uses_and_sizes_the_cache():
     for gx, gs in grads[1:]:
         assert float((gx - grads[0][0]).abs().max()) <= 2e-6 * float(grads[0][0].abs().max())
         assert float((gs - grads[0][1]).abs().max()) <= 2e-6 * float(grads[0][1].abs().max())
+
+
+def test_sweeps_interleaved_on_two_streams_match_the_single_stream_result():
+    """Every sweep draws its rows from its own pair of ticket words; sweeps issued alternately on two streams
+    (so that they can overlap on the GPU) must give the results of the same calls made one after the other,
+    and leave every ticket word zero."""
+    from npa_b200 import _native as n, sphops as sph
+    w = Workload("two_streams", dim=3, B=2, N=6000, C=16, eps=0.12, grid_size=(10, 10, 10))
+    x, s, _ = make_inputs(w, seed=4)
+    grid = make_grid(sph, w)
+    snap = grid.instantiate(x.cuda())
+    xb, sb = sph.bin_particles(x.cuda(), s.cuda(), snap)
+    rho = sph.density(xb, snap)
+    want_blur, want_grad = sph.blur(xb, rho, sb, snap), sph.gradient(xb, rho, sb, snap)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = []
+    for k in range(40):
+        with torch.cuda.stream(streams[k % 2]):
+            outs.append((sph.blur(xb, rho, sb, snap), sph.gradient(xb, rho, sb, snap)))
+    torch.cuda.synchronize()
+    for blur, grad in outs:
+        assert torch.equal(blur, want_blur) and torch.equal(grad, want_grad)
+    assert n.row_tickets_nonzero() == 0

@@ -61,9 +61,11 @@ def _grid(c):
                         num_particles=c["N"], batch_size=c["B"], max_particles_per_block=32)
 
 
-def _close(a, b, what, rtol=1e-5, atol=1e-6):
-    """Two fp32 evaluations of the same formulas (operator by operator with torch glue, and fused):
-    held to the stated bar, 1e-5 relative / 1e-6 of the tensor's scale, elementwise."""
+def _close(a, b, what, rtol=2e-5, atol=2e-6):
+    """Two fp32 evaluations of the same formulas (operator by operator with torch glue, and fused).  Each
+    side is held to 1e-5 relative / 1e-6 of the tensor's scale against the fp64 truth elsewhere
+    (tests/test_gpu_ops_oracle.py, tests/test_gpu_fusion.py), so the two may differ from one another by
+    twice that: 2e-5 relative / 2e-6 of the scale, elementwise."""
     a, b = a.detach().double(), b.detach().double()
     scale = float(b.abs().max())
     err = (a - b).abs()

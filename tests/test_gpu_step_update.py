@@ -205,3 +205,42 @@ def test_step_euler_equals_the_operator_sequence(dim):
     for a, b in zip(*results):
         scale = float(b.abs().max())
         assert float((a - b).abs().max()) <= 2e-5 * scale + 1e-30, (a.shape, float((a - b).abs().max()), scale)
+
+
+def test_step_euler_makes_no_host_synchronisation_after_the_first_step():
+    """eps0 / alpha of the model are device buffers; the step reads them once and caches the floats, so a
+    training loop does not stall its launch queue on a device-to-host copy every step (the reference keeps
+    them on the device and never synchronises in step_euler)."""
+    from npa_b200 import sphops as sph
+    from npa_b200.stepping import step_euler
+
+    class Model(torch.nn.Module):
+        def __init__(self, dim, C):
+            super().__init__()
+            self.spatial_dims, self.state_dims = dim, C
+            self.register_buffer("eps0", torch.tensor([0.1]))
+            self.register_buffer("alpha", torch.tensor([1.0]))
+            width = 2 * C + C * dim + dim
+            self.model = torch.nn.Sequential(torch.nn.Linear(width, 128), torch.nn.ReLU(),
+                                             torch.nn.Linear(128, dim + C, bias=False))
+
+    dim, C = 2, 16
+    model = Model(dim, C).cuda()
+    grid = sph.HashGrid(dim=dim, boundary="periodic", mode="grid", grid_size=(10, 10), eps=0.2, num_particles=2048,
+                        batch_size=2, max_particles_per_block=32)
+    g = torch.Generator().manual_seed(0)
+    x = ((torch.rand(2, 2048, dim, generator=g) - 0.5) * 2.0).cuda()
+    s = torch.randn(2, 2048, C, generator=g).cuda()
+    step_euler(model, x, s, grid, update_prob=1.0)      # first step: reads the buffers, sizes the launches
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        x1, s1, _ = step_euler(model, x, s, grid, update_prob=1.0)
+        x2, s2, _ = step_euler(model, x1, s1, grid, update_prob=1.0)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    assert torch.isfinite(x2).all() and torch.isfinite(s2).all()
+    model.alpha.mul_(0.5)                               # an in-place change of the buffer is picked up
+    x3, _, _ = step_euler(model, x, s, grid, update_prob=1.0)
+    assert not torch.equal(x3, x1)
