@@ -58,6 +58,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the strong-scaling shards and the reference-kernel comparator")
+    ap.add_argument("--tile-forward", default=None, metavar="ROWS,PARTICLES,STAGES,WARPS,CELLS",
+                    help="run the blur+gradient forward sweep on the cell-tile streaming engine with this tuning "
+                         "(0 = automatic), e.g. 448,32,2,24,2")
+    ap.add_argument("--tile-backward", default=None, metavar="ROWS,PARTICLES,STAGES,WARPS,CELLS",
+                    help="same for the backward sweep, e.g. 128,32,2,8,2")
     return ap.parse_args()
 
 
@@ -486,6 +491,10 @@ def run_gpu_arm(args, w):
         raise RuntimeError("bench.py needs a CUDA device: the npa_b200 kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    from npa_b200 import _native
+    for backward, spec in ((False, args.tile_forward), (True, args.tile_backward)):
+        if spec:
+            _native.tile_tuning(backward, True, *[int(v) for v in spec.split(",")])
     if world > 1:
         from npa_b200.sharding import bind_to_gpu_cpus
         bound = bind_to_gpu_cpus(local_rank)  # pinned buffers below land on the GPU's NUMA node
@@ -644,6 +653,7 @@ def run_gpu_arm(args, w):
             "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(w),
+            "tile_engine": {"forward": args.tile_forward, "backward": args.tile_backward},
             "parallelism": f"{world} x independent batches of {B} systems (weak scaling)",
             "phase_ms": phase_ms,
             "binning_mpoints_per_s": B * N / ((phase_ms["grid_build"] + phase_ms["reorder"]) * 1e-3) / 1e6,
