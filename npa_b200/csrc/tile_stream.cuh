@@ -10,8 +10,8 @@
 // load/store pipe of the consumers.
 //
 // Flow control is two mbarriers per stage: `full` (producer arrives with the byte count, the copies
-// complete it) and `empty` (one arrival per consumer warp).  No copy uses cluster multicast and every
-// tensor is memory of this GPU.  Every wait is bounded: after kTileWaitNs of unsuccessful polling a
+// complete it) and `empty` (one arrival per consumer warp).  Every copy lands in the issuing CTA's own shared memory
+// only, and every tensor is memory of this GPU.  Every wait is bounded: after kTileWaitNs of unsuccessful polling a
 // thread records a code in the status word, stops waiting and the CTA drains to its exit.
 //
 // Alignment: bulk copies need 16-byte aligned addresses and sizes.  Feature rows are C floats with
@@ -109,7 +109,7 @@ __device__ inline bool mbar_wait(uint64_t *bar, unsigned parity, unsigned long l
     }
 }
 // Global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned); completion
-// is counted on `bar`.  No multicast: the destination is this CTA's own shared memory.
+// is counted on `bar`.  The destination is this CTA's own shared memory and nothing else.
 __device__ inline void bulk_copy_g2s(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      smem_u32(dst)),
