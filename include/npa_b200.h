@@ -436,6 +436,30 @@ int npa_linear_tf32x3(const float *A, const float *W, const float *bias, const f
                       int64_t w_stride_in, int32_t relu, void *stream);
 
 /*
+ * The same product as npa_linear_tf32x3 on the fifth-generation tensor cores: tcgen05.mma with the
+ * accumulators in tensor memory, operands split into TF32 head and tail (three MMAs per product, fp32
+ * accuracy), tiles of 128 rows, one persistent warp-specialised CTA per SM.  in_dim <= 1024 and
+ * out_dim <= 256 (else NPA_ERR_UNSUPPORTED).  `scratch` is device memory of at least
+ * npa_linear_tcgen05_scratch_bytes(in_dim, out_dim) bytes, 16-byte aligned, private to the call
+ * until its kernels have run: it receives the split, swizzled image of the weights.  Two launches on
+ * `stream`.  Every wait inside the kernel is bounded in time; npa_linear_tcgen05_status() copies the
+ * device status word to the host (0 = no wait ever gave up; bits 1, 2, 4, 8 = the MMA warp, the
+ * weight copies, the producers, the epilogue) and clears it when `reset` is non-zero; it
+ * synchronises the device.  Replaces the SIMT fp32 GEMMs of the adaptation MLP
+ * (models/npa.py:63-75,143) like npa_linear_tf32x3.
+ */
+int64_t npa_linear_tcgen05_scratch_bytes(int32_t in_dim, int32_t out_dim);
+int npa_linear_tcgen05(const float *A, const float *W, const float *bias, const float *gate, float *C,
+                       int64_t rows, int32_t in_dim, int32_t out_dim, int64_t w_stride_out,
+                       int64_t w_stride_in, int32_t relu, void *scratch, int64_t scratch_bytes, void *stream);
+int npa_linear_tcgen05_status(uint32_t *host_status, int32_t reset);
+/* Self-test of those bounded waits: a two-warp kernel in which warp 0 waits `limit_us` (1..1,000,000)
+ * on an mbarrier that nothing completes, gives up and raises the kernel's leave flag, and warp 1,
+ * waiting on a second such mbarrier with the full limit, leaves through the flag.  device_result[0]
+ * and [1] (device memory) both read 1 afterwards; the context stays usable. */
+int npa_linear_tcgen05_wait_selftest(int32_t limit_us, int32_t *device_result, void *stream);
+
+/*
  * Cell-tile streaming engine of the blur + gradient sweeps (no counterpart in the reference's
  * binding; the reference stages neighbour cells per block inside forward_kernel / backward_kernel,
  * sphops/sph_cuda.cu:1561-1660, 903-1160, without a switch).

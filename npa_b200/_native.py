@@ -85,6 +85,11 @@ SIGNATURES = {
                                            _P, _P, _P, _P]),
     "npa_linear_tf32x3": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
                                          _I32, _P]),
+    "npa_linear_tcgen05": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
+                                          _I32, _P, ctypes.c_int64, _P]),
+    "npa_linear_tcgen05_scratch_bytes": (ctypes.c_int64, [_I32, _I32]),
+    "npa_linear_tcgen05_status": (ctypes.c_int, [_P, _I32]),
+    "npa_linear_tcgen05_wait_selftest": (ctypes.c_int, [_I32, _P, _P]),
     "npa_step_update_backward": (ctypes.c_int, [_P] * 3 + [_I32, ctypes.c_float, ctypes.c_float, _P, _P, _P, _P]),
     "npa_tile_tuning": (ctypes.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
     "npa_tile_status": (ctypes.c_int, [_P, _I32]),

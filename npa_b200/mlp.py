@@ -2,8 +2,9 @@
 
 The reference's MLP (models/npa.py:63-75) is ``Linear(in, hidden) -> ReLU -> Linear(hidden, out,
 bias=False)`` applied to every particle.  Its two forward GEMMs and the two input-gradient GEMMs
-run on the tensor cores at fp32 accuracy (``npa_linear_tf32x3``: three TF32 MMAs per product on
-split operands, bias and ReLU in the epilogue); the gradients of the weights -- three reductions
+run on the tensor cores at fp32 accuracy (three TF32 MMAs per product on split operands, bias and
+ReLU in the epilogue): ``npa_linear_tcgen05`` (tcgen05.mma, accumulators in tensor memory) by
+default, ``npa_linear_tf32x3`` (``mma.sync``) when ``TENSOR_ENGINE = "mma.sync"``; the gradients of the weights -- three reductions
 over all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one
 CUDA-core kernel (``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` computed
 this way when ``module`` has the reference's structure and a hidden width of 128, and plain
@@ -19,6 +20,7 @@ _lib = N.lib
 HIDDEN = 128
 MAX_IN, MAX_OUT = 176, 48
 MIN_TENSOR_DIM = 64   # narrower products go to the library
+TENSOR_ENGINE = "tcgen05"   # or "mma.sync": which kernel runs the wide products
 GATED_DH_ON_TENSOR_CORES = False  # dh = (dy W2) gated by h in one tensor-core kernel: measured slower (1.42 vs 1.35 ms per MLP pass) than the thin library GEMM + a mask pass
 
 
@@ -39,8 +41,14 @@ def _linear(a, w, bias, relu, w_is_out_by_in, gate=None, force_tensor=False):
     stride_out, stride_in = (w.stride(0), w.stride(1)) if w_is_out_by_in else (w.stride(1), w.stride(0))
     c = torch.empty(m, n, dtype=torch.float32, device=a.device)
     with torch.cuda.device(a.device):
-        N.check(_lib.npa_linear_tf32x3(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(gate), N.ptr(c), m, k, n, stride_out, stride_in,
-                                       1 if relu else 0, N.current_stream()))
+        if TENSOR_ENGINE == "tcgen05":
+            nbytes = _lib.npa_linear_tcgen05_scratch_bytes(k, n)
+            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=a.device)  # weight image, private to the call
+            N.check(_lib.npa_linear_tcgen05(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(gate), N.ptr(c), m, k, n, stride_out,
+                                            stride_in, 1 if relu else 0, N.ptr(scratch), nbytes, N.current_stream()))
+        else:
+            N.check(_lib.npa_linear_tf32x3(N.ptr(a), N.ptr(w), N.ptr(bias), N.ptr(gate), N.ptr(c), m, k, n, stride_out,
+                                           stride_in, 1 if relu else 0, N.current_stream()))
     return c
 
 

@@ -1,10 +1,25 @@
-"""The adaptation MLP on the tensor-core linear kernel (npa_linear_tf32x3: three TF32 MMAs per
-product) and the fused weight-gradient kernel (npa_mlp_weight_grad) against torch: values and
-gradients held to float64 truth about as tightly as torch's own float32 run."""
+"""The adaptation MLP on the tensor-core linear kernels (three TF32 MMAs per product:
+npa_linear_tcgen05 with the accumulators in tensor memory, and npa_linear_tf32x3 on mma.sync) and the
+fused weight-gradient kernel (npa_mlp_weight_grad) against torch: values and gradients held to
+float64 truth about as tightly as torch's own float32 run.  Every test runs once per engine."""
+import ctypes
+
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=["tcgen05", "mma.sync"])
+def engine(request, monkeypatch):
+    import npa_b200.mlp as mlp
+    monkeypatch.setattr(mlp, "TENSOR_ENGINE", request.param)
+    yield request.param
+    if request.param == "tcgen05":   # no bounded wait of the kernel ever gave up
+        from npa_b200 import _native as n
+        status = ctypes.c_uint32(0)
+        n.check(n.lib.npa_linear_tcgen05_status(ctypes.byref(status), 1))
+        assert status.value == 0, f"linear_umma_kernel reported status {status.value}"
 
 
 def _mlp(k, o, hidden=128, seed=0):
@@ -65,10 +80,14 @@ def test_two_runs_are_bit_identical_and_unsupported_shapes_fall_back():
 
 @pytest.mark.parametrize("rows,k,n,out_by_in,relu,bias", [(1000, 163, 128, True, True, True), (777, 128, 35, True, False, False),
                                                           (4096, 35, 128, False, False, False), (130, 128, 163, False, False, False),
-                                                          (64, 176, 128, True, True, True), (5, 3, 1, True, False, True)])
-def test_linear_kernel_against_float64(rows, k, n, out_by_in, relu, bias):
-    """npa_linear_tf32x3 alone, both weight layouts, odd sizes, partial tiles."""
+                                                          (64, 176, 128, True, True, True), (5, 3, 1, True, False, True),
+                                                          (128 * 148 * 2 + 77, 163, 128, True, True, True),
+                                                          (40000, 128, 163, False, False, False), (300, 200, 256, True, False, True)])
+def test_linear_kernel_against_float64(rows, k, n, out_by_in, relu, bias, engine):
+    """The linear kernel alone, both weight layouts, odd sizes, partial tiles, more tiles than CTAs."""
     from npa_b200.mlp import _linear
+    if engine == "mma.sync" and max(k, n) > 176:
+        pytest.skip("the mma.sync kernel holds the whole weight matrix in shared memory: up to 176 x 176")
     g = torch.Generator(device="cuda").manual_seed(2)
     a = torch.randn(rows, k, generator=g, device="cuda")
     w = torch.randn((n, k) if out_by_in else (k, n), generator=g, device="cuda")
@@ -97,3 +116,17 @@ def test_gated_linear_is_the_relu_backward():
         got = _linear(dy, w2, None, False, False, gate=h, force_tensor=force)
         assert float((got.double() - want).abs().max()) <= 4e-6 * float(want.abs().max())
         assert torch.equal(got == 0, want == 0) or float(((got == 0) != (want == 0)).float().mean()) < 1e-6
+
+
+def test_a_wait_that_runs_out_ends_the_tcgen05_kernel_roles_cleanly(engine):
+    """The bounded waits of linear_umma_kernel: a wait on an mbarrier that nothing completes gives up after
+    its limit and raises the leave flag; a second role waiting elsewhere leaves through the flag; the
+    context stays usable (no trap, no fault, no endless loop)."""
+    if engine != "tcgen05":
+        pytest.skip("the mma.sync kernel has no mbarrier waits")
+    from npa_b200 import _native as n
+    res = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    n.check(n.lib.npa_linear_tcgen05_wait_selftest(2000, n.ptr(res), n.current_stream()))
+    torch.cuda.synchronize()
+    assert res.tolist() == [1, 1]
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
