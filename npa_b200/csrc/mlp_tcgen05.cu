@@ -25,6 +25,8 @@
 //
 // Every wait on an mbarrier is bounded in time; a wait that gives up raises a flag that ends all
 // roles, the CTA frees its tensor memory and the host reads the reason from a status word.
+#include <mutex>
+
 #include "tile_stream.cuh"
 
 namespace npa {
@@ -220,8 +222,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
                     tc_fence_after();
                     const uint64_t a_hi = desc0 + stage16 * s, a_lo = a_hi + alo16, b_hi = a_hi + bhi16, b_lo = a_hi + blo16;
                     const int ksteps = c == nchunks - 1 ? last_ksteps : kUmmaChunk / 8;
-#pragma unroll 1
-                    for (int ks = 0; ks < ksteps; ++ks) {
+#pragma unroll
+                    for (int ks = 0; ks < kUmmaChunk / 8; ++ks) {
+                        if (ks >= ksteps) break;
                         const uint64_t o = 2ull * ks;  // 8 floats = 32 bytes further along K, in 16-byte units
                         umma_tf32(d, a_lo + o, b_hi + o, idesc, (c | ks) != 0);
                         umma_tf32(d, a_hi + o, b_lo + o, idesc, 1);
@@ -302,21 +305,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
             }
             return true;
         };
-        // three chunks in flight: v0 is stored while v1 and v2 are still on their way
+        // Three chunks in flight in three register sets that take turns (no register is copied: a copy
+        // would wait for the load it reads and end the overlap).
         float v0[8], v1[8], v2[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v0[j] = v1[j] = v2[j] = 0.f;
         if (0 < total) load(v0);
         if (1 < total) load(v1);
 #pragma unroll 1
-        for (int q = 0; q < total; ++q) {
+        for (int q = 0; q < total; q += 3) {
             if (q + 2 < total) load(v2);
             if (!(ok = store(v0))) break;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v0[j] = v1[j];
-                v1[j] = v2[j];
-            }
+            if (q + 1 >= total) break;
+            if (q + 3 < total) load(v0);
+            if (!(ok = store(v1))) break;
+            if (q + 2 >= total) break;
+            if (q + 4 < total) load(v1);
+            if (!(ok = store(v2))) break;
         }
         if (!ok && lane == 0) atomicOr(status, UMMA_STATUS_PRODUCER);
     } else {
@@ -431,6 +434,33 @@ __global__ void umma_wait_selftest_kernel(unsigned long long limit_ns, int *resu
     if ((threadIdx.x & 31) == 0) result[warp] = completed ? 0 : (warp == 0 || by_flag ? 1 : 2);
 }
 
+// Per-device set-up done once: the address of the status word and the shared-memory limit of the kernel.
+struct UmmaDevice {
+    unsigned *status = nullptr;
+    int smem_limit = 0;
+};
+static std::mutex g_umma_mutex;
+static UmmaDevice g_umma_device[64];
+
+static int umma_device_setup(int smem, unsigned **status) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(NPA_ERR_CUDA, "npa_linear_tcgen05: cudaGetDevice: %s", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(g_umma_mutex);
+    UmmaDevice &d = g_umma_device[dev];
+    if (!d.status) {
+        e = cudaGetSymbolAddress((void **)&d.status, g_umma_status);
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_linear_tcgen05: status word: %s", cudaGetErrorString(e));
+    }
+    if (smem > d.smem_limit) {
+        e = cudaFuncSetAttribute(linear_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_linear_tcgen05: raising the shared-memory limit: %s", cudaGetErrorString(e));
+        d.smem_limit = smem;
+    }
+    *status = d.status;
+    return NPA_OK;
+}
+
 static int umma_round16(int v) { return (v + 15) / 16 * 16; }
 static int umma_chunks(int k) { return (k + kUmmaChunk - 1) / kUmmaChunk; }
 
@@ -470,14 +500,12 @@ int npa_linear_tcgen05(const float *A, const float *W, const float *bias, const 
     if (a.stages > kUmmaMaxStages) a.stages = kUmmaMaxStages;
     if (a.stages < 2) return fail(NPA_ERR_UNSUPPORTED, "npa_linear_tcgen05: out_dim %d leaves room for fewer than two stages", out_dim);
     const size_t smem = (size_t)fixed + (size_t)a.stages * a.stage_bytes;
-    cudaError_t e = cudaGetSymbolAddress((void **)&a.status, g_umma_status);
-    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_linear_tcgen05: status word: %s", cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(linear_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(NPA_ERR_CUDA, "npa_linear_tcgen05: raising the shared-memory limit: %s", cudaGetErrorString(e));
+    int rc = umma_device_setup((int)smem, &a.status);
+    if (rc != NPA_OK) return rc;
     const int total = a.nchunks * a.Np * kUmmaChunk;
     weight_image_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(W, w_stride_out, w_stride_in, in_dim, out_dim, a.Np,
                                                                                  a.nchunks, (float *)scratch);
-    int rc = check_launch("weight_image_kernel");
+    rc = check_launch("weight_image_kernel");
     if (rc != NPA_OK) return rc;
     const long long tiles = (rows + kUmmaRows - 1) / kUmmaRows;
     const int ctas = (int)(tiles < 148 ? tiles : 148);
