@@ -358,7 +358,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
                                                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                 __syncwarp();
                 if (vec4) {
-                    const int c4 = 4 * (lane & 3), sub = lane >> 2;  // eight rows x four float4 per instruction
+                    // eight rows x four float4 per instruction; the two rows of a quarter-warp are four staged
+                    // rows apart (4 x 20 floats = 16 banks), so that its eight float4 cover all 32 banks
+                    const int c4 = 4 * (lane & 3), t = lane >> 2, sub = (t >> 1) + 4 * (t & 1);
                     if (c0 + c4 < N) {
                         const float4 bv = *(const float4 *)(sh->bias + c0 + c4);
 #pragma unroll
