@@ -422,6 +422,17 @@ int npa_mlp_weight_grad(const float *z, const float *dh, const float *h, const f
                         int32_t in_dim, int32_t hidden, int32_t out_dim, float *scratch, int64_t scratch_floats,
                         float *dW1, float *dW2, float *db1, void *stream);
 
+/* The same three reductions on the fifth-generation tensor cores (tcgen05.mma, TF32 head / tail
+ * products, accumulators in tensor memory drained into fp32 partial sums every 128 rows so that no
+ * accumulation chain of the tensor cores is longer than 48 MMAs).  Same arguments and results as
+ * npa_mlp_weight_grad; in <= 175, out <= 48, hidden 128; inputs and scratch 16-byte aligned,
+ * scratch with npa_mlp_weight_grad_tcgen05_scratch_floats() floats.  Bounded waits report through
+ * npa_linear_tcgen05_status (bits 16, 32, 64: MMA lane, producers, epilogue of this kernel). */
+int64_t npa_mlp_weight_grad_tcgen05_scratch_floats(int64_t rows, int32_t in_dim, int32_t out_dim);
+int npa_mlp_weight_grad_tcgen05(const float *z, const float *dh, const float *h, const float *dy, int64_t rows,
+                                int32_t in_dim, int32_t hidden, int32_t out_dim, float *scratch,
+                                int64_t scratch_floats, float *dW1, float *dW2, float *db1, void *stream);
+
 /* ---- linear layers of the MLP on the tensor cores, fp32 accuracy ----------------- *
  *   C [rows, out] = act( A [rows, in] . B + bias ),  B[k][n] = W[n * w_stride_out + k * w_stride_in]
  * with act = ReLU when relu != 0; bias [out] may be NULL; with gate [rows, out] != NULL the output

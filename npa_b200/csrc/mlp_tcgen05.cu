@@ -27,7 +27,7 @@
 // roles, the CTA frees its tensor memory and the host reads the reason from a status word.
 #include <mutex>
 
-#include "tile_stream.cuh"
+#include "umma.cuh"
 
 namespace npa {
 
@@ -43,7 +43,6 @@ constexpr int kUmmaAccStride = 256;
 constexpr int kUmmaTileABytes = kUmmaRows * kUmmaChunk * 4;  // one operand tile of A: 16 KB
 constexpr int kUmmaEpiPitch = 20;         // floats per staged row of 16 columns: 16-byte aligned, conflict-free float4 writes
 constexpr int kUmmaEpiFloats = kUmmaEpilogueWarps * 32 * kUmmaEpiPitch;
-constexpr unsigned long long kUmmaWaitNs = 2000000000ull;
 
 enum { UMMA_STATUS_MMA = 1, UMMA_STATUS_WEIGHTS = 2, UMMA_STATUS_PRODUCER = 4, UMMA_STATUS_EPILOGUE = 8 };
 
@@ -66,76 +65,6 @@ struct UmmaArgs {
 };
 
 __device__ unsigned g_umma_status;
-
-// ---- tcgen05 primitives -------------------------------------------------------------------------
-__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ inline void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ inline void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// Shared-memory operand descriptor of a K-major tile with 128-byte rows and the 128-byte swizzle:
-// rows 128 bytes apart, groups of eight rows 1024 bytes apart, tile base 1024-byte aligned.
-__device__ inline uint64_t umma_desc(unsigned smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-// D[tmem] (+)= A[smem] . B[smem]^T, TF32 operands, fp32 accumulation; issued by one thread.
-__device__ inline void umma_tf32(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, unsigned idesc, int accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
-__device__ inline void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ inline void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-// Bounded wait that also ends when another role has given up.  The first thread to run out of time
-// raises the flag; false means "leave".  Hand-offs between the roles take well under a microsecond, so
-// the wait polls and looks at the clock only every 64 polls; it is one copy of code for all roles
-// (the kernel runs four different instruction streams at once and has to stay small).
-__device__ inline bool umma_try_wait(uint64_t *bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-__device__ __noinline__ bool umma_wait_slow(uint64_t *bar, unsigned parity, int *abort_flag, unsigned long long limit_ns) {
-    unsigned long long t0 = 0;
-#pragma unroll 1
-    for (unsigned spins = 1;; ++spins) {
-        if (umma_try_wait(bar, parity)) return true;
-        if ((spins & 63u) == 0) {
-            if (*(volatile int *)abort_flag) return false;
-            const unsigned long long now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > limit_ns) {
-                *(volatile int *)abort_flag = 1;
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ bool umma_wait(uint64_t *bar, unsigned parity, int *abort_flag, unsigned long long limit_ns = kUmmaWaitNs) {
-    if (umma_try_wait(bar, parity)) return true;
-    return umma_wait_slow(bar, parity, abort_flag, limit_ns);
-}
-
-// Position (in floats) of element (row, k) of a K-major operand tile with 128-byte rows under the
-// 128-byte swizzle: the 16-byte unit index is XORed with the row index modulo 8.
-__host__ __device__ inline int umma_swizzled(int row, int k) { return row * 32 + ((((k >> 2) ^ (row & 7)) << 2) | (k & 3)); }
-
-__device__ inline unsigned tf32_head_bits(float x) { return __float_as_uint(x) & 0xffffe000u; }
 
 // Head and tail images of the weights, chunk by chunk, in the layout the MMA reads.
 __global__ void weight_image_kernel(const float *W, long long stride_n, long long stride_k, int K, int N, int Np, int nchunks,
@@ -461,6 +390,12 @@ static int umma_device_setup(int smem, unsigned **status) {
     }
     *status = d.status;
     return NPA_OK;
+}
+
+// Device address of the status word on the current device (also used by mlp_grad_tcgen05.cu).
+unsigned *umma_status_word() {
+    unsigned *p = nullptr;
+    return cudaGetSymbolAddress((void **)&p, g_umma_status) == cudaSuccess ? p : nullptr;
 }
 
 static int umma_round16(int v) { return (v + 15) / 16 * 16; }

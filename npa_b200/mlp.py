@@ -4,9 +4,11 @@ The reference's MLP (models/npa.py:63-75) is ``Linear(in, hidden) -> ReLU -> Lin
 bias=False)`` applied to every particle.  Its two forward GEMMs and the two input-gradient GEMMs
 run on the tensor cores at fp32 accuracy (three TF32 MMAs per product on split operands, bias and
 ReLU in the epilogue): ``npa_linear_tcgen05`` (tcgen05.mma, accumulators in tensor memory) by
-default, ``npa_linear_tf32x3`` (``mma.sync``) when ``TENSOR_ENGINE = "mma.sync"``; the gradients of the weights -- three reductions
-over all ``B * N`` rows, half of the MLP's forward + backward time in torch -- come from one
-CUDA-core kernel (``npa_mlp_weight_grad``).  ``apply_mlp(module, z)`` returns ``module(z)`` computed
+default, ``npa_linear_tf32x3`` (``mma.sync``) when ``TENSOR_ENGINE = "mma.sync"``; the gradients of
+the weights -- three reductions over all ``B * N`` rows, half of the MLP's forward + backward time
+in torch -- come from one kernel: ``npa_mlp_weight_grad_tcgen05`` (the same tensor cores,
+accumulation chains of 128 rows added in fp32) by default, the CUDA-core ``npa_mlp_weight_grad`` with
+the other engine.  ``apply_mlp(module, z)`` returns ``module(z)`` computed
 this way when ``module`` has the reference's structure and a hidden width of 128, and plain
 ``module(z)`` otherwise.
 """
@@ -19,6 +21,7 @@ from . import _native as N
 _lib = N.lib
 HIDDEN = 128
 MAX_IN, MAX_OUT = 176, 48
+MAX_IN_TCGEN05 = 175  # the tcgen05 weight-gradient kernel appends a column of ones to z: in + 1 <= 176
 MIN_TENSOR_DIM = 64   # narrower products go to the library
 TENSOR_ENGINE = "tcgen05"   # or "mma.sync": which kernel runs the wide products
 GATED_DH_ON_TENSOR_CORES = False  # dh = (dy W2) gated by h in one tensor-core kernel: measured slower (1.42 vs 1.35 ms per MLP pass) than the thin library GEMM + a mask pass
@@ -73,12 +76,14 @@ class _AdaptationMLP(torch.autograd.Function):
         if need_w1 or need_b1 or need_w2:
             m, k, o = rows.shape[0], rows.shape[1], w2.shape[0]
             g_w1, g_b1, g_w2 = torch.empty_like(w1), torch.empty(HIDDEN, dtype=w1.dtype, device=w1.device), torch.empty_like(w2)
-            n_scratch = _lib.npa_mlp_weight_grad_scratch_floats(m, k, o)
+            on_tcgen05 = TENSOR_ENGINE == "tcgen05" and k <= MAX_IN_TCGEN05
+            sizer, kernel = ((_lib.npa_mlp_weight_grad_tcgen05_scratch_floats, _lib.npa_mlp_weight_grad_tcgen05) if on_tcgen05
+                             else (_lib.npa_mlp_weight_grad_scratch_floats, _lib.npa_mlp_weight_grad))
+            n_scratch = sizer(m, k, o)
             scratch = torch.empty(n_scratch, dtype=torch.float32, device=rows.device)
             with torch.cuda.device(rows.device):
-                N.check(_lib.npa_mlp_weight_grad(N.ptr(rows), N.ptr(dh), N.ptr(h), N.ptr(dy), m, k, HIDDEN, o,
-                                                 N.ptr(scratch), n_scratch, N.ptr(g_w1), N.ptr(g_w2), N.ptr(g_b1),
-                                                 N.current_stream()))
+                N.check(kernel(N.ptr(rows), N.ptr(dh), N.ptr(h), N.ptr(dy), m, k, HIDDEN, o, N.ptr(scratch), n_scratch,
+                               N.ptr(g_w1), N.ptr(g_w2), N.ptr(g_b1), N.current_stream()))
         return g_z, (g_w1 if need_w1 else None), (g_b1 if need_b1 else None), (g_w2 if need_w2 else None)
 
 
