@@ -70,7 +70,18 @@ def test_npa_perceive_sequence_fused_equals_unfused(fusion, dim, boundary, stopg
         assert torch.allclose(gxf, gxu, rtol=1e-4, atol=1e-5 * float(gxu.abs().max()))
 
 
-def test_parked_outputs_are_only_claimed_by_the_same_inputs(fusion):
+@pytest.fixture
+def per_particle_density_sweep():
+    """The density-only sweep shares candidates between the particles of a tile and sums in another order
+    than the per-particle sweep the fused call (density + density gradient) runs: with the shared sweep
+    switched off a claimed output is bit-identical to the operator's own launch."""
+    from npa_b200 import _native as n
+    n.check(n.lib.npa_scalar_sweep_tuning(0))
+    yield
+    n.check(n.lib.npa_scalar_sweep_tuning(3))
+
+
+def test_parked_outputs_are_only_claimed_by_the_same_inputs(fusion, per_particle_density_sweep):
     sph = fusion
     w = Workload("park", dim=2, B=1, N=1500, C=8, eps=0.06, grid_size=(18, 18))
     x, s, _ = make_inputs(w, seed=5)

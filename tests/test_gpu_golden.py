@@ -63,9 +63,12 @@ def test_forward_against_reference_outputs(name):
     for k in ("rho", "rho_grad", "blur", "grad", "moment"):
         out = np64(_unbin(got[k], perm))
         assert_parity(out, arr[f"f64_{k}"], arr[f"f32_{k}"], what=f"{name}:{k} vs fp64 reference")
-    # the fused forward gives the same tensors as the single operators
+    # the fused forward gives the same tensors as the single operators; the density-only sweep may share
+    # candidates between the particles of a tile and then adds a particle's pairs in another order than the
+    # fused sweep: equal to two roundings there, bit-identical everywhere else
     rho_f, blur_f, grad_f, dg_f = sph.perceive(xb, sb, snap, mb)
-    assert torch.equal(rho_f, got["rho"]) and torch.equal(dg_f, got["rho_grad"])
+    assert torch.allclose(rho_f, got["rho"], rtol=2e-6, atol=0.0) and torch.equal(dg_f, got["rho_grad"])
+    assert_parity(np64(_unbin(rho_f, perm)), arr["f64_rho"], arr["f32_rho"], what=f"{name}:fused rho vs fp64 reference")
     assert torch.equal(blur_f, sph.blur(xb, rho_f, sb, snap, mb))
     assert torch.equal(grad_f, sph.gradient(xb, rho_f, sb, snap, mb))
 
