@@ -464,6 +464,19 @@ int npa_linear_tcgen05(const float *A, const float *W, const float *bias, const 
                        int64_t rows, int32_t in_dim, int32_t out_dim, int64_t w_stride_out,
                        int64_t w_stride_in, int32_t relu, void *scratch, int64_t scratch_bytes, void *stream);
 int npa_linear_tcgen05_status(uint32_t *host_status, int32_t reset);
+/* Both layers of the adaptation MLP's forward in the same kernel (models/npa.py:63-75,143):
+ *   h [rows, 128] = relu(z [rows, in] . W1^T + b1),   y [rows, out] = h . W2^T   (no bias on the second layer)
+ * with h kept in tensor memory between the layers: the epilogue activates the first layer's tile in
+ * place, adds its TF32 tail next to it, and the second product reads both from tensor memory as its A
+ * operand (W2 resident in shared memory).  h is also stored (the backward needs it).  Hidden width 128,
+ * in <= 1024, out <= 64; W1 [128, in] and W2 [out, 128] are addressed through their strides; scratch of
+ * npa_mlp_forward_tcgen05_scratch_bytes() bytes, 16-byte aligned; three launches on `stream`; bounded waits
+ * and status as npa_linear_tcgen05. */
+int64_t npa_mlp_forward_tcgen05_scratch_bytes(int32_t in_dim, int32_t out_dim);
+int npa_mlp_forward_tcgen05(const float *z, const float *W1, const float *b1, const float *W2, float *h, float *y,
+                            int64_t rows, int32_t in_dim, int32_t out_dim, int64_t w1_stride_out,
+                            int64_t w1_stride_in, int64_t w2_stride_out, int64_t w2_stride_in, void *scratch,
+                            int64_t scratch_bytes, void *stream);
 /* Self-test of those bounded waits: a two-warp kernel in which warp 0 waits `limit_us` (1..1,000,000)
  * on an mbarrier that nothing completes, gives up and raises the kernel's leave flag, and warp 1,
  * waiting on a second such mbarrier with the full limit, leaves through the flag.  device_result[0]

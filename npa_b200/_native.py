@@ -90,6 +90,8 @@ SIGNATURES = {
                                          _I32, _P]),
     "npa_linear_tcgen05": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64,
                                           _I32, _P, ctypes.c_int64, _P]),
+    "npa_mlp_forward_tcgen05": (ctypes.c_int, [_P] * 6 + [ctypes.c_int64, _I32, _I32] + [ctypes.c_int64] * 4 + [_P, ctypes.c_int64, _P]),
+    "npa_mlp_forward_tcgen05_scratch_bytes": (ctypes.c_int64, [_I32, _I32]),
     "npa_linear_tcgen05_scratch_bytes": (ctypes.c_int64, [_I32, _I32]),
     "npa_linear_tcgen05_status": (ctypes.c_int, [_P, _I32]),
     "npa_linear_tcgen05_wait_selftest": (ctypes.c_int, [_I32, _P, _P]),

@@ -24,6 +24,7 @@ MAX_IN, MAX_OUT = 176, 48
 MAX_IN_TCGEN05 = 175  # the tcgen05 weight-gradient kernel appends a column of ones to z: in + 1 <= 176
 MIN_TENSOR_DIM = 64   # narrower products go to the library
 TENSOR_ENGINE = "tcgen05"   # or "mma.sync": which kernel runs the wide products
+FUSED_FORWARD = True        # tcgen05 engine: both layers of the forward in one kernel (h kept in tensor memory)
 GATED_DH_ON_TENSOR_CORES = False  # dh = (dy W2) gated by h in one tensor-core kernel: measured slower (1.42 vs 1.35 ms per MLP pass) than the thin library GEMM + a mask pass
 
 
@@ -59,8 +60,20 @@ class _AdaptationMLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, z, w1, b1, w2):
         rows = z.reshape(-1, z.shape[-1])
-        h = _linear(rows, w1, b1, True, True)
-        y = _linear(h, w2, None, False, True)
+        m, k, o = rows.shape[0], rows.shape[1], w2.shape[0]
+        if TENSOR_ENGINE == "tcgen05" and FUSED_FORWARD and o <= 64:
+            # both layers in one kernel: h stays in tensor memory between them (it is also stored for the backward)
+            h = torch.empty(m, HIDDEN, dtype=torch.float32, device=rows.device)
+            y = torch.empty(m, o, dtype=torch.float32, device=rows.device)
+            nbytes = _lib.npa_mlp_forward_tcgen05_scratch_bytes(k, o)
+            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=rows.device)
+            with torch.cuda.device(rows.device):
+                N.check(_lib.npa_mlp_forward_tcgen05(N.ptr(rows), N.ptr(w1), N.ptr(b1), N.ptr(w2), N.ptr(h), N.ptr(y), m, k, o,
+                                                     w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1), N.ptr(scratch), nbytes,
+                                                     N.current_stream()))
+        else:
+            h = _linear(rows, w1, b1, True, True)
+            y = _linear(h, w2, None, False, True)
         ctx.save_for_backward(rows, h, w1, w2)
         ctx.z_shape = z.shape
         return y.reshape(*z.shape[:-1], w2.shape[0])
