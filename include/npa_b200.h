@@ -422,6 +422,13 @@ int npa_mlp_weight_grad(const float *z, const float *dh, const float *h, const f
                         int32_t in_dim, int32_t hidden, int32_t out_dim, float *scratch, int64_t scratch_floats,
                         float *dW1, float *dW2, float *db1, void *stream);
 
+/* Gradient at the hidden layer with the ReLU mask: dh [rows, 128] = (dy [rows, out] . W2 [out, 128]) where
+ * h > 0, else 0 -- the backward of Linear(128, out, bias = False) and of the ReLU that produced h
+ * (models/npa.py:63-75) in one pass (torch: a thin GEMM plus a masking pass).  fp32 on the CUDA cores.
+ * hidden must be 128, out <= 48; W2 is addressed through its strides; h and dh 16-byte aligned. */
+int npa_mlp_hidden_grad(const float *dy, const float *W2, const float *h, float *dh, int64_t rows,
+                        int32_t hidden, int32_t out_dim, int64_t w_stride_out, int64_t w_stride_in, void *stream);
+
 /* The same three reductions on the fifth-generation tensor cores (tcgen05.mma, TF32 head / tail
  * products, accumulators in tensor memory drained into fp32 partial sums every 128 rows so that no
  * accumulation chain of the tensor cores is longer than 48 MMAs).  Same arguments and results as

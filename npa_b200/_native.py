@@ -83,6 +83,7 @@ SIGNATURES = {
     "npa_mlp_weight_grad_scratch_floats": (ctypes.c_int64, [ctypes.c_int64, _I32, _I32]),
     "npa_mlp_weight_grad": (ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int64, _I32, _I32, _I32, _P, ctypes.c_int64,
                                            _P, _P, _P, _P]),
+    "npa_mlp_hidden_grad": (ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int64, _I32, _I32, ctypes.c_int64, ctypes.c_int64, _P]),
     "npa_mlp_weight_grad_tcgen05": (ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int64, _I32, _I32, _I32, _P, ctypes.c_int64,
                                                    _P, _P, _P, _P]),
     "npa_mlp_weight_grad_tcgen05_scratch_floats": (ctypes.c_int64, [ctypes.c_int64, _I32, _I32]),

@@ -24,6 +24,7 @@ MAX_IN, MAX_OUT = 176, 48
 MAX_IN_TCGEN05 = 175  # the tcgen05 weight-gradient kernel appends a column of ones to z: in + 1 <= 176
 MIN_TENSOR_DIM = 64   # narrower products go to the library
 TENSOR_ENGINE = "tcgen05"   # or "mma.sync": which kernel runs the wide products
+FUSED_HIDDEN_GRAD = True    # dh = (dy W2) with the ReLU mask in one pass on the CUDA cores
 FUSED_FORWARD = True        # tcgen05 engine: both layers of the forward in one kernel (h kept in tensor memory)
 GATED_DH_ON_TENSOR_CORES = False  # dh = (dy W2) gated by h in one tensor-core kernel: measured slower (1.42 vs 1.35 ms per MLP pass) than the thin library GEMM + a mask pass
 
@@ -83,7 +84,14 @@ class _AdaptationMLP(torch.autograd.Function):
         rows, h, w1, w2 = ctx.saved_tensors
         need_z, need_w1, need_b1, need_w2 = ctx.needs_input_grad
         dy = g_y.reshape(-1, g_y.shape[-1]).contiguous()
-        dh = _linear(dy, w2, None, False, False, gate=h, force_tensor=GATED_DH_ON_TENSOR_CORES)  # ReLU mask from h
+        if FUSED_HIDDEN_GRAD and w2.shape[0] <= MAX_OUT:
+            # dh = (dy W2) masked by h > 0 in one pass (fp32, CUDA cores) instead of a thin GEMM plus a masking pass
+            dh = torch.empty_like(h)
+            with torch.cuda.device(h.device):
+                N.check(_lib.npa_mlp_hidden_grad(N.ptr(dy), N.ptr(w2), N.ptr(h), N.ptr(dh), dy.shape[0], HIDDEN, w2.shape[0],
+                                                 w2.stride(0), w2.stride(1), N.current_stream()))
+        else:
+            dh = _linear(dy, w2, None, False, False, gate=h, force_tensor=GATED_DH_ON_TENSOR_CORES)  # ReLU mask from h
         g_z = _linear(dh, w1, None, False, False).reshape(ctx.z_shape) if need_z else None
         g_w1 = g_b1 = g_w2 = None
         if need_w1 or need_b1 or need_w2:
