@@ -59,7 +59,7 @@ enum { UMMA_STATUS_MMA = 1, UMMA_STATUS_WEIGHTS = 2, UMMA_STATUS_PRODUCER = 4, U
 
 struct UmmaShared {
     uint64_t full[kUmmaMaxStages], empty[kUmmaMaxStages], acc_full[2], acc_empty[2];
-    uint64_t h_ready[2], y_full, w2_full;  // two-layer mode only
+    uint64_t h_ready[2], y_full, w2_full, y_written, y_copied;  // two-layer mode only
     uint32_t tmem_base;
     int abort;
     alignas(16) float bias[256];
@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
     uint8_t *w2s = base + (size_t)stages * stage_bytes;   // two-layer mode: the whole image of W2, resident
     const int w2_bytes = fuse ? 4 * 2 * N2p * 128 : 0;
     float *epi = (float *)(w2s + w2_bytes);
-    UmmaShared *sh = (UmmaShared *)(epi + kUmmaEpiFloats);
+    float *ytile = epi + kUmmaEpiFloats;                  // two-layer mode: the second layer's tile, rows of N2 floats as in global memory
+    UmmaShared *sh = (UmmaShared *)(ytile + (fuse ? ((kUmmaRows * N2 + 3) & ~3) : 0));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -136,6 +137,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
         }
         mbar_init(&sh->y_full, 1);
         mbar_init(&sh->w2_full, 1);
+        mbar_init(&sh->y_written, kUmmaEpilogueWarps);
+        mbar_init(&sh->y_copied, kUmmaEpilogueWarps);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -340,6 +343,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
                     if (!(ok = umma_wait(pass == 2 ? &sh->y_full : &sh->acc_full[acc], pass == 2 ? it & 1 : (it >> 1) & 1, &sh->abort))) break;
                     tc_fence_after();
                 }
+                // the previous tile's rows have left the shared-memory tile
+                if (fuse && pass == 2 && !(ok = umma_wait(&sh->y_copied, (it & 1) ^ 1, &sh->abort))) break;
                 int last_block = first_block;
                 while (last_block + 2 < nblocks) last_block += 2;
 #pragma unroll 1
@@ -354,17 +359,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
                         if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
                     }
                     if (fuse && pass == 2) {
-                        // the second layer's tile: the sum of its two accumulators, stored straight from the registers (lane =
-                        // row; rows of N2 floats are too short and too few for the trip through shared memory to pay)
+                        // the second layer's tile: the sum of its two accumulators goes into a shared-memory tile laid out
+                        // like the tile's rows in global memory (they are contiguous there), copied out linearly below
                         unsigned r2[16];
                         tmem_ld16(tlane + kUmmaY2Col + c0, r2);
                         tc_wait_ld();
-                        if (lane < nrows) {
-                            float *yrow = out + (row0 + lane) * ncol + c0;
+                        float *yrow = ytile + (quarter * 32 + lane) * ncol + c0;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c0 + j < ncol) yrow[j] = __uint_as_float(r[j]) + __uint_as_float(r2[j]);
-                        }
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < ncol) yrow[j] = __uint_as_float(r[j]) + __uint_as_float(r2[j]);
                         continue;
                     }
                     if (act_here) {
@@ -437,6 +440,24 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) linear_umma_kernel(const __gr
                         }
                     }
                     __syncwarp();
+                }
+                if (fuse && pass == 2) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->y_written);
+                    if (!(ok = umma_wait(&sh->y_written, it & 1, &sh->abort))) break;
+                    // all eight warps copy the tile: (rows that exist) x N2 floats, contiguous and 16-byte aligned in global memory
+                    const long long tile_row0 = ((long long)blockIdx.x + (long long)it * gridDim.x) * kUmmaRows;
+                    const int rows_here = M - tile_row0 < kUmmaRows ? (int)(M - tile_row0) : kUmmaRows;
+                    const int total = rows_here * ncol, e = warp * 32 + lane;
+                    float *dst = out + tile_row0 * ncol;
+                    if (((uintptr_t)out & 15) == 0) {
+                        for (int q = e; q < total / 4; q += kUmmaEpilogueWarps * 32) ((float4 *)dst)[q] = ((const float4 *)ytile)[q];
+                        for (int q = (total & ~3) + e; q < total; q += kUmmaEpilogueWarps * 32) dst[q] = ytile[q];
+                    } else {
+                        for (int q = e; q < total; q += kUmmaEpilogueWarps * 32) dst[q] = ytile[q];
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->y_copied);
                 }
                 if (act_here) {  // h and its tail are in tensor memory: the second layer (and pass 1) may read them
                     tc_wait_st();
@@ -591,7 +612,7 @@ int npa_mlp_forward_tcgen05(const float *z, const float *W1, const float *b1, co
     a.Y = y; a.N2 = out_dim; a.N2p = umma_round16(out_dim);
     a.W2img = (const float *)((const char *)scratch + npa_linear_tcgen05_scratch_bytes(in_dim, kUmmaRows));
     const int w2_bytes = 4 * 2 * a.N2p * 128;
-    const int fixed = 1024 + kUmmaEpiFloats * 4 + (int)sizeof(UmmaShared) + w2_bytes;
+    const int fixed = 1024 + kUmmaEpiFloats * 4 + (int)sizeof(UmmaShared) + w2_bytes + ((kUmmaRows * out_dim + 3) & ~3) * 4;
     a.stages = (227 * 1024 - fixed) / a.stage_bytes;
     if (a.stages > kUmmaMaxStages) a.stages = kUmmaMaxStages;
     if (a.stages < 2) return fail(NPA_ERR_UNSUPPORTED, "%s: no room for two stages", me);

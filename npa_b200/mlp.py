@@ -62,7 +62,7 @@ class _AdaptationMLP(torch.autograd.Function):
     def forward(ctx, z, w1, b1, w2):
         rows = z.reshape(-1, z.shape[-1])
         m, k, o = rows.shape[0], rows.shape[1], w2.shape[0]
-        if TENSOR_ENGINE == "tcgen05" and FUSED_FORWARD and o <= 64:
+        if TENSOR_ENGINE == "tcgen05" and FUSED_FORWARD and o <= MAX_OUT:
             # both layers in one kernel: h stays in tensor memory between them (it is also stored for the backward)
             h = torch.empty(m, HIDDEN, dtype=torch.float32, device=rows.device)
             y = torch.empty(m, o, dtype=torch.float32, device=rows.device)
