@@ -215,3 +215,49 @@ def test_linear_tf32x3_rejects_unsupported_shapes_before_any_launch():
     assert call(1000, 176, 176) == n.NPA_ERR_UNSUPPORTED and "shared memory" in n.last_error()
     assert call(0, 128, 128) == n.NPA_ERR_INVALID_ARGUMENT
     assert call(1000, 128, 128, null) == n.NPA_ERR_INVALID_ARGUMENT
+
+
+def test_tcgen05_entry_points_reject_bad_arguments_before_any_launch():
+    """The tensor-memory kernels validate shapes, pointers, alignment and scratch size on the host: an
+    operand or instruction descriptor outside its range would lose the CUDA context, so nothing may launch."""
+    from npa_b200 import _native as n
+    lib = n.lib
+    buf, odd, null = ctypes.c_void_p(256), ctypes.c_void_p(260), ctypes.c_void_p(0)
+    big = 1 << 40
+    # linear layer
+    assert lib.npa_linear_tcgen05_scratch_bytes(163, 128) == 6 * 2 * 128 * 32 * 4
+    assert lib.npa_linear_tcgen05_scratch_bytes(128, 163) == 4 * 2 * 176 * 32 * 4
+    lin = lambda rows, k, o, a=buf, scratch=buf, nbytes=big: lib.npa_linear_tcgen05(a, buf, null, null, buf, rows, k, o, k, 1, 0, scratch, nbytes, null)
+    assert lin(1000, 128, 257) == n.NPA_ERR_UNSUPPORTED and "out_dim" in n.last_error()
+    assert lin(1000, 1025, 128) == n.NPA_ERR_UNSUPPORTED
+    assert lin(0, 128, 128) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lin(1000, 128, 128, a=null) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lin(1000, 128, 128, scratch=odd) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lin(1000, 128, 128, nbytes=16) == n.NPA_ERR_INVALID_ARGUMENT and "scratch" in n.last_error()
+    # both layers of the forward
+    assert lib.npa_mlp_forward_tcgen05_scratch_bytes(163, 35) == 6 * 2 * 128 * 32 * 4 + 4 * 2 * 48 * 32 * 4
+    fwd = lambda rows, k, o, z=buf, nbytes=big: lib.npa_mlp_forward_tcgen05(z, buf, buf, buf, buf, buf, rows, k, o, k, 1, 128, 1, buf, nbytes, null)
+    assert fwd(1000, 163, 65) == n.NPA_ERR_UNSUPPORTED
+    assert fwd(1000, 1025, 35) == n.NPA_ERR_UNSUPPORTED
+    assert fwd(-1, 163, 35) == n.NPA_ERR_INVALID_ARGUMENT
+    assert fwd(1000, 163, 35, z=null) == n.NPA_ERR_INVALID_ARGUMENT
+    assert fwd(1000, 163, 35, nbytes=1024) == n.NPA_ERR_INVALID_ARGUMENT
+    # weight gradients
+    assert lib.npa_mlp_weight_grad_tcgen05_scratch_floats(262144, 163, 35) == 148 * 128 * (176 + 48)
+    wg = lambda rows, k, h, o, z=buf, floats=big: lib.npa_mlp_weight_grad_tcgen05(z, buf, buf, buf, rows, k, h, o, buf, floats, buf, buf, buf, null)
+    assert wg(1000, 66, 64, 18) == n.NPA_ERR_UNSUPPORTED and "hidden" in n.last_error()
+    assert wg(1000, 176, 128, 18) == n.NPA_ERR_UNSUPPORTED      # in + 1 columns must fit six atoms of 32
+    assert wg(1000, 66, 128, 49) == n.NPA_ERR_UNSUPPORTED
+    assert wg(0, 66, 128, 18) == n.NPA_ERR_INVALID_ARGUMENT
+    assert wg(1000, 66, 128, 18, z=odd) == n.NPA_ERR_INVALID_ARGUMENT and "aligned" in n.last_error()
+    assert wg(1000, 66, 128, 18, floats=10) == n.NPA_ERR_SCRATCH_TOO_SMALL
+    # hidden-layer gradient
+    hg = lambda rows, h, o, dh=buf: lib.npa_mlp_hidden_grad(buf, buf, buf, dh, rows, h, o, 128, 1, null)
+    assert hg(1000, 64, 18) == n.NPA_ERR_UNSUPPORTED
+    assert hg(1000, 128, 49) == n.NPA_ERR_UNSUPPORTED
+    assert hg(0, 128, 18) == n.NPA_ERR_INVALID_ARGUMENT
+    assert hg(1000, 128, 18, dh=odd) == n.NPA_ERR_INVALID_ARGUMENT
+    # status and self-test arguments
+    assert lib.npa_linear_tcgen05_status(null, 0) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lib.npa_linear_tcgen05_wait_selftest(0, buf, null) == n.NPA_ERR_INVALID_ARGUMENT
+    assert lib.npa_linear_tcgen05_wait_selftest(2000, null, null) == n.NPA_ERR_INVALID_ARGUMENT
