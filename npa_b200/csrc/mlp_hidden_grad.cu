@@ -106,7 +106,7 @@ int npa_mlp_hidden_grad(const float *dy, const float *W2, const float *h, float 
     HiddenGradArgs a = {dy, W2, h, dh, rows, w_stride_out, w_stride_in, out_dim, (out_dim + 3) / 4 * 4};
     const long long groups = (rows + kHgRows - 1) / kHgRows;
     const long long want = (groups + kHgWarps - 1) / kHgWarps;
-    const int ctas = (int)(want < 148 * 4 ? want : 148 * 4);
+    const int ctas = (int)(want < 148 * 3 ? want : 148 * 3);  // 84 registers x 256 threads: three CTAs per SM, one wave
     mlp_hidden_grad_kernel<<<ctas, kHgThreads, 0, (cudaStream_t)stream>>>(a);
     return check_launch("mlp_hidden_grad_kernel");
 }
