@@ -165,6 +165,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
         const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
         float mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // F_MOMENT: upper triangle, lane-partial over pairs
+        float dgs[3] = {0.f, 0.f, 0.f};                   // F_PACK with rho_grad_out: density gradient, lane-partial over pairs
         for (int fbase = 0; fbase < C; fbase += LPP * VW) {
             const int f0 = fbase + sl * VW;
             const bool fvalid = f0 < C;
@@ -193,7 +194,14 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     }
                     if ((MASK & (F_GRAD | F_MOMENT)) && q > 0.f) {
                         float dist;
-                        kv = vj * spiky_phi(q, g.h, dist);
+                        const float phi = spiky_phi(q, g.h, dist);
+                        kv = vj * phi;
+                        if ((MASK & F_PACK) && a.rho_grad_out && fbase == 0) {  // the density gradient's pair term: m_j phi r
+                            const float w = mj * phi;
+                            dgs[0] = fmaf(w, ge.x, dgs[0]);
+                            dgs[1] = fmaf(w, ge.y, dgs[1]);
+                            if (D == 3) dgs[2] = fmaf(w, ge.z, dgs[2]);
+                        }
                     }
                     if ((MASK & F_MOMENT) && fbase == 0) {  // every pair is seen once per feature chunk
                         mom[0] = fmaf(kv * ge.x, ge.x, mom[0]);
@@ -327,10 +335,23 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                         for (int d = 0; d < D; ++d) zs[2 * C + f * D + d] = v[d];
                     }
                 }
+                if (a.rho_grad_out) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) dgs[d] = g.c_g * subgroup_sum<32>(dgs[d]);
+                }
                 if (lane == 0) {
                     float w[D];
 #pragma unroll
-                    for (int d = 0; d < D; ++d) w[d] = __ldg(a.rho_grad + i * D + d) * a.dg_scale;
+                    for (int d = 0; d < D; ++d) {
+                        float dgd;
+                        if (a.rho_grad_out) {
+                            dgd = dgs[d];
+                            a.rho_grad_out[i * D + d] = dgd;  // the backward pass reads it
+                        } else {
+                            dgd = __ldg(a.rho_grad + i * D + d);
+                        }
+                        w[d] = dgd * a.dg_scale;
+                    }
                     if (a.log_norm_dg) log_normalize<D>(w);
 #pragma unroll
                     for (int d = 0; d < D; ++d) zs[2 * C + C * D + d] = w[d];

@@ -12,6 +12,7 @@ enum { S_COUNT = 1, S_DENSITY = 2, S_DGRAD = 4, S_MOMENT = 8 };
 // F_PACK (forward only, with all three others) applies the perception epilogue per particle and
 // writes the packed perception vector instead of the separate tensors.
 enum { F_BLUR = 1, F_GRAD = 2, F_MOMENT = 4, F_PACK = 8 };
+bool tile_forward_enabled();  // tile_host.cu: the cell-tile streaming engine is switched on for forward sweeps
 
 struct ScalarFwdArgs {
     const float *x;       // [B,N,P] cell order
@@ -61,7 +62,8 @@ struct FeatureFwdArgs {
     float *z;                // [B,N,zstride], zstride = 2C + C*D + D
     int zstride;
     float *vgrad;            // [B,N,C,D] or NULL: grad_i @ safe_inv(M_i), kept for the backward pass
-    const float *rho_grad;   // [B,N,D] density gradient of the same positions
+    const float *rho_grad;   // [B,N,D] density gradient of the same positions, or NULL when rho_grad_out is set
+    float *rho_grad_out;     // [B,N,D] or NULL: the packed sweep computes the density gradient itself and writes it here
     float coef, dg_scale, inv_tol;
     int log_norm_grad, log_norm_dg;
     // ---- neighbour list cache (optional): row i = [count | j_0 .. j_{count-1}], count = -1 when the

@@ -67,6 +67,8 @@ bool tile_make_layout(int P, bool with_mass, int floats_s, int floats_gb, int fl
 // Off by default: on the measured workloads the gather kernels are as fast or faster (the sweeps are
 // bound by instruction issue, not by the L2 -> SM traffic the staging saves).
 static TileTuning g_tuning[2] = {{0, 0, 0, 0, kTileWarpsDefault, 0}, {0, 0, 0, 0, kTileWarpsDefault, 0}};
+bool tile_forward_enabled() { return tile_tuning(false).enabled != 0; }
+
 TileTuning tile_tuning(bool backward) { return g_tuning[backward ? 1 : 0]; }
 
 // ---- status word ------------------------------------------------------------------------------
