@@ -68,7 +68,7 @@ class PerceptionRollout:
         self.grad_rho = torch.empty(B, N, **f32)
         self.grad_x_in = torch.empty(B, N, P, **f32)
         self.grad_s_in = torch.empty(B, N, channels, **f32)
-        self.pairs = torch.empty(B, N, 64, **i32)  # neighbour lists of the last step, shared by its four sweeps
+        self.pairs = torch.empty(B, N, 64, **i32)  # neighbour lists of the current step, shared by its sweeps
         self.half_box = None
         if grid.boundary == "periodic":
             self.box = torch.tensor([g * grid.eps for g in grid.grid_size[:D]], **f32)
@@ -81,11 +81,13 @@ class PerceptionRollout:
         hg = self.hg
         hg.initialize(x, self.perm, self.offs, self.info)
         hg.bin_particles(x, s, None, self.perm, self.x_bin, self.s_bin, None)
-        pairs = self.pairs if last else None  # the lists pay off only where a backward follows
+        # the density sweep records the neighbour lists in every step: writing them costs 15 % of that sweep, and
+        # the blur + gradient sweep that reads them takes less than half the time of one that searches the cells
+        # itself (cfg5's shape, 3D periodic: 1.05 + 1.09 ms against 0.91 + 2.42 ms per million particles)
         hg.perception_forward(self.x_bin, None, None, self.rho, None, None, None, None, None, self.offs, self.info,
-                              pair_cache=pairs)
+                              pair_cache=self.pairs)
         hg.blur_gradient_forward(self.x_bin, self.rho, None, self.s_bin, self.blur, self.grad, self.offs, self.info,
-                                 pair_cache=pairs, pair_cache_valid=last)
+                                 pair_cache=self.pairs, pair_cache_valid=True)
 
     def _move(self, x, s):
         """x <- wrap(x_bin + dt * v(x_bin)), s <- s_bin: the particles continue in cell order."""
