@@ -44,10 +44,13 @@ class PerceptionRollout:
 
     ``x`` is ``[B, N, P]`` (P = 2, or 4 in 3D), ``s`` is ``[B, N, C]``; both are overwritten by the
     particles in the cell order of the last step.  ``upstream`` holds the gradients of the last
-    step's outputs (``g_rho [B,N]``, ``g_blur [B,N,C]``, ``g_grad [B,N,C,D]``).
+    step's outputs (``g_rho [B,N]``, ``g_blur [B,N,C]``, ``g_grad [B,N,C,D]``).  ``list_slots`` is the row
+    length of the neighbour lists (one count + up to ``list_slots - 1`` neighbours, at most 129); particles
+    with more neighbours fall back to the cell search.
     """
 
-    def __init__(self, grid: "sph.HashGrid", channels: int, steps: int, dt: float, velocity: VelocityField):
+    def __init__(self, grid: "sph.HashGrid", channels: int, steps: int, dt: float, velocity: VelocityField,
+                 list_slots: int = 64):
         self.grid, self.hg = grid, grid.hashgrid
         self.steps, self.dt, self.velocity = int(steps), float(dt), velocity
         B, N, D = grid.batch_size, grid.num_particles, grid.dim
@@ -68,7 +71,7 @@ class PerceptionRollout:
         self.grad_rho = torch.empty(B, N, **f32)
         self.grad_x_in = torch.empty(B, N, P, **f32)
         self.grad_s_in = torch.empty(B, N, channels, **f32)
-        self.pairs = torch.empty(B, N, 64, **i32)  # neighbour lists of the current step, shared by its sweeps
+        self.pairs = torch.empty(B, N, list_slots, **i32)  # neighbour lists of the current step, shared by its sweeps
         self.half_box = None
         if grid.boundary == "periodic":
             self.box = torch.tensor([g * grid.eps for g in grid.grid_size[:D]], **f32)
