@@ -262,9 +262,14 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             };
             int listed = -1;
             if (a.pair_cache && a.pair_cache_valid) listed = __ldg(a.pair_cache + i * a.pair_stride);
-            if (listed >= 0 && listed <= kListPerWarp) {
-                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
-                flush(listed);
+            if (listed >= 0) {
+                // a list longer than the warp's pair slots goes through in pieces (the sums carry over)
+                const int32_t *list = a.pair_cache + i * a.pair_stride + 1;
+                for (int off = 0; off < listed || off == 0; off += kListPerWarp) {
+                    const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
+                    expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
+                    flush(n);
+                }
             } else {
                 collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
                 if (a.pair_cache && !a.pair_cache_valid && fbase == 0 && lane == 0)
@@ -594,9 +599,14 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             };
             int listed = -1;
             if (a.pair_cache) listed = __ldg(a.pair_cache + i * a.pair_stride);
-            if (listed >= 0 && listed <= kListPerWarp) {
-                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
-                flush(listed);
+            if (listed >= 0) {
+                // a list longer than the warp's pair slots goes through in pieces (the sums carry over)
+                const int32_t *list = a.pair_cache + i * a.pair_stride + 1;
+                for (int off = 0; off < listed || off == 0; off += kListPerWarp) {
+                    const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
+                    expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
+                    flush(n);
+                }
             } else {
                 collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
             }

@@ -155,3 +155,26 @@ def test_sweeps_interleaved_on_two_streams_match_the_single_stream_result():
     for blur, grad in outs:
         assert torch.equal(blur, want_blur) and torch.equal(grad, want_grad)
     assert n.row_tickets_nonzero() == 0
+
+
+@pytest.mark.parametrize("boundary", ["clamped", "periodic"])
+def test_lists_longer_than_the_pair_slots_of_a_warp(boundary):
+    """A crowded system (~180 neighbours per particle in the interior): with 257 columns most lists are longer than the 128
+    pair slots a warp of the blur + gradient sweeps holds and go through in pieces; the results are those
+    of the cell search."""
+    from npa_b200 import sphops as sph
+    w = Workload("pc_dense_" + boundary, dim=3, B=1, N=2800, C=8, eps=0.25, grid_size=(4, 4, 4), boundary=boundary)
+    grid, snap, x_bin, s_bin = _binned(sph, w, seed=21)
+    g = torch.Generator().manual_seed(6)
+    ups = {"g_rho": torch.randn(w.B, w.N, generator=g).cuda(),
+           "g_blur": torch.randn(w.B, w.N, w.C, generator=g).cuda(),
+           "g_grad": torch.randn(w.B, w.N, w.C, w.dim, generator=g).cuda()}
+    base, _ = _native_sequence(w, grid, snap, x_bin, s_bin, 0, ups)
+    got, pairs = _native_sequence(w, grid, snap, x_bin, s_bin, 257, ups)
+    counts = pairs[..., 0]
+    listed = counts[counts >= 0]
+    assert int((listed > 128).sum()) > 0.3 * counts.numel(), "most lists should need more than one piece"
+    for k in base:
+        scale = float(base[k].abs().max())
+        err = float((got[k] - base[k]).abs().max())
+        assert err <= 2e-6 * scale, (k, err, scale)
