@@ -415,8 +415,9 @@ def strong_scaling(rank, world, dev):
     grid = sph.HashGrid(dim=ws.dim, boundary=ws.boundary, mode=ws.mode, grid_size=ws.grid_size, eps=ws.eps,
                         num_particles=ws.N, batch_size=ws.B, max_particles_per_block=ws.max_particles_per_block)
     # the velocity field gathers the particles into clumps over the 64 steps (at the end three particles in four have
-    # more than 63 neighbours, one in four more than 255): long lists keep them out of the cell search (-19 % per rollout)
-    roll = PerceptionRollout(grid, ws.C, steps=steps, dt=dt, velocity=VelocityField(ws.dim, dev, seed=5), list_slots=256)
+    # more than 63 neighbours, one in four more than 255, one in seventeen more than 383): long lists keep them out of
+    # the cell search (-23 % per rollout against 63 slots)
+    roll = PerceptionRollout(grid, ws.C, steps=steps, dt=dt, velocity=VelocityField(ws.dim, dev, seed=5), list_slots=384)
     x, s = x0.clone(), s0.clone()
 
     def rollout():

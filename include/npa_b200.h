@@ -254,7 +254,7 @@ int npa_safe_inv_sym_mat(int32_t dim, int64_t n, const float *m, float *m_inv,
  * sweeps) rebuilds the displacements from the list instead of testing the ~3^D
  * cells of candidates again (particles marked -1 are searched as usual).
  * The cache belongs to one snapshot AND one set of positions.  2 <= pair_stride
- * <= 257.  No counterpart in the reference.                                   */
+ * <= 513.  No counterpart in the reference.                                   */
 
 /* ---- blur + gradient in one launch ------------------------------------------ *
  * The two feature operators share every pair test and every neighbour feature

@@ -131,8 +131,8 @@ static int check_channels(const char *name, int C) {
 }
 
 static int check_pair_cache(const char *name, const void *cache, int stride) {
-    if (cache && (stride < 2 || stride > 257))
-        return fail(NPA_ERR_INVALID_ARGUMENT, "%s: pair_stride must be in [2, 257], got %d", name, stride);
+    if (cache && (stride < 2 || stride > 513))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "%s: pair_stride must be in [2, 513], got %d", name, stride);
     return NPA_OK;
 }
 

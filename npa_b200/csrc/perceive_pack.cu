@@ -97,8 +97,8 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
     if (((uintptr_t)x_bin % (g.dim == 2 ? 8 : 16)) || ((uintptr_t)block_info % 16))
         return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: positions / block_info are misaligned");
     cudaStream_t st = (cudaStream_t)stream;
-    if (pair_cache && (pair_stride < 2 || pair_stride > 257))
-        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 257]");
+    if (pair_cache && (pair_stride < 2 || pair_stride > 513))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 513]");
     // The packed sweep meets every pair with its spiky kernel value in hand, so it also sums the density
     // gradient; the first sweep is then the density alone (and the neighbour lists), which the shared-
     // candidate kernel runs in about half the time of the density + density-gradient sweep.  With the
@@ -117,8 +117,8 @@ int npa_perceive_features_forward(const npa_grid *gd, int32_t channels, const fl
     fa.inv_tol = inv_tol;
     fa.log_norm_grad = log_norm_grad;
     fa.log_norm_dg = log_norm_dg;
-    if (pair_cache && (pair_stride < 2 || pair_stride > 257))
-        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 257]");
+    if (pair_cache && (pair_stride < 2 || pair_stride > 513))
+        return fail(NPA_ERR_INVALID_ARGUMENT, "perceive_features_forward: pair_stride must be in [2, 513]");
     fa.pair_cache = pair_cache;
     fa.pair_stride = pair_stride;
     fa.pair_cache_valid = pair_cache != nullptr;  // written by the density sweep above

@@ -45,7 +45,7 @@ class PerceptionRollout:
     ``x`` is ``[B, N, P]`` (P = 2, or 4 in 3D), ``s`` is ``[B, N, C]``; both are overwritten by the
     particles in the cell order of the last step.  ``upstream`` holds the gradients of the last
     step's outputs (``g_rho [B,N]``, ``g_blur [B,N,C]``, ``g_grad [B,N,C,D]``).  ``list_slots`` is the row
-    length of the neighbour lists (one count + up to ``list_slots - 1`` neighbours, at most 257); particles
+    length of the neighbour lists (one count + up to ``list_slots - 1`` neighbours, at most 513); particles
     with more neighbours fall back to the cell search.
     """
 

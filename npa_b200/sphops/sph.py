@@ -142,8 +142,8 @@ def set_pair_cache(columns=64):
     """Size of the per-particle neighbour list the fused forward sweeps keep for their backward
     (4 * columns bytes per particle while the autograd graph is alive); 0 disables it."""
     columns = int(columns)
-    if columns != 0 and not 2 <= columns <= 257:
-        raise ValueError("columns must be 0 or between 2 and 257")
+    if columns != 0 and not 2 <= columns <= 513:
+        raise ValueError("columns must be 0 or between 2 and 513")
     _PAIR_CACHE["columns"] = columns
 
 

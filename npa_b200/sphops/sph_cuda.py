@@ -112,13 +112,13 @@ class _HashGridBase:
         return self._scratch
 
     def _pairs(self, pair_cache):
-        """(pointer, stride) of an optional neighbour-list cache ``[B, N, K]`` int32, 2 <= K <= 257."""
+        """(pointer, stride) of an optional neighbour-list cache ``[B, N, K]`` int32, 2 <= K <= 513."""
         if pair_cache is None:
             return None, 0
         K = pair_cache.shape[-1] if isinstance(pair_cache, torch.Tensor) and pair_cache.dim() == 3 else -1
         _check(pair_cache, (self._B, self._N, K), "pair_cache", torch.int32)
-        if not 2 <= K <= 257:
-            raise RuntimeError(f"pair_cache must have between 2 and 257 columns, got {K}")
+        if not 2 <= K <= 513:
+            raise RuntimeError(f"pair_cache must have between 2 and 513 columns, got {K}")
         return N.ptr(pair_cache), K
 
     @staticmethod
