@@ -537,7 +537,10 @@ def run_gpu_arm(args, w):
     blur = torch.empty(B, N, C, **f32)
     grad = torch.empty(B, N, C, D, **f32)
     grad_x, grad_s, grad_rho = torch.empty_like(x_d), torch.empty_like(s_d), torch.empty(B, N, **f32)
-    pairs = torch.empty(B, N, 64, **i32)  # neighbour lists: written by the density sweep, read by the other three
+    # neighbour lists: written by the density sweep, read by the other three.  127 slots: with 63, one particle in 600
+    # of this workload overflows, and in the density backward (eight particles per warp pass) every pass that holds
+    # such a particle walks the cells for all of its lanes: 108 -> 82 us
+    pairs = torch.empty(B, N, 128, **i32)
     mlp_grad = torch.zeros(MLP_GRAD_FLOATS, **f32)
     comm = torch.cuda.Stream(dev) if world > 1 else None      # the gradient all-reduce runs beside the sweeps
     step_done = torch.cuda.Event()

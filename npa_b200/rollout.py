@@ -50,7 +50,7 @@ class PerceptionRollout:
     """
 
     def __init__(self, grid: "sph.HashGrid", channels: int, steps: int, dt: float, velocity: VelocityField,
-                 list_slots: int = 64):
+                 list_slots: int = 128):
         self.grid, self.hg = grid, grid.hashgrid
         self.steps, self.dt, self.velocity = int(steps), float(dt), velocity
         B, N, D = grid.batch_size, grid.num_particles, grid.dim

@@ -135,10 +135,10 @@ class HashGrid:
 _FUSION = {"enabled": False}
 # Columns of the neighbour-list cache the fused forward passes write for their backward pass
 # (row = count, j_0, j_1, ...; particles with more neighbours are searched again); 0 = off.
-_PAIR_CACHE = {"columns": 64}
+_PAIR_CACHE = {"columns": 128}
 
 
-def set_pair_cache(columns=64):
+def set_pair_cache(columns=128):
     """Size of the per-particle neighbour list the fused forward sweeps keep for their backward
     (4 * columns bytes per particle while the autograd graph is alive); 0 disables it."""
     columns = int(columns)
