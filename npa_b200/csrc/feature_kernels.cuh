@@ -604,16 +604,19 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
             };
             int listed = -1;
             if (a.pair_cache) listed = __ldg(a.pair_cache + i * a.pair_stride);
-            if (listed >= 0) {
-                // a list longer than the warp's pair slots goes through in pieces (the sums carry over)
+            if (listed >= 0 && listed <= kListPerWarp) {
+                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
+                flush(listed);
+            } else if (listed > kListPerWarp) {
+                // a list longer than the warp's pair slots goes through in pieces (the sums carry over); kept apart
+                // from the common case above (a loop around it slows the sweeps that have few registers to spare)
                 const int32_t *list = a.pair_cache + i * a.pair_stride + 1;
-                int off = 0;
-                do {
+#pragma unroll 1
+                for (int off = 0; off < listed; off += kListPerWarp) {
                     const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
                     expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
                     flush(n);
-                    off += kListPerWarp;
-                } while (off < listed);
+                }
             } else {
                 collect_pairs<D, PER>(g, a.x, pi, rng, nr, geo, flush);
             }
