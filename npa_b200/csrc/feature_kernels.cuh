@@ -217,6 +217,8 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     }
                     ent[e] = make_float4(kv * ge.x, kv * ge.y, kv * ge.z, wv);
                 }
+                // zero weights fill the last pass of stage 3 (n <= kListPerWarp, a multiple of PP: the slots exist)
+                if (n + lane < (n + PP - 1) / PP * PP) ent[n + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
                 __syncwarp();
                 if (fvalid) {
                     // stage 3: each sub-group drains every PP-th pair; the neighbour's feature rows pass
@@ -235,26 +237,30 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                         }
                     };
                     {
+                        // row address = lane base + index x row pitch: one wide multiply-add per load
+                        const char *srow = reinterpret_cast<const char *>(a.s + f0);
+                        const unsigned pitch = (unsigned)C * 4u;
                         auto load = [&](int e, float (&sj)[VW]) {
-                            if (e < n) load_feat<VW>(a.s + ((long long)__float_as_int(geo[e].w) * C + f0), sj);
+                            if (e < n)
+                                load_feat<VW>(reinterpret_cast<const float *>(
+                                                  srow + (unsigned long long)(unsigned)__float_as_int(geo[e].w) * pitch), sj);
                         };
+                        // every sub-group makes the same number of passes (the entries that fill the last pass
+                        // have zero weights), so the loop has no divergent exit
                         float r0[VW] = {}, r1[VW] = {}, r2[VW] = {};
-                        int e = sg;
+                        int e = sg, left = (n + PP - 1) / PP;
                         load(e, r0);
                         load(e + PP, r1);
-                        while (e < n) {
+                        for (; left >= 3; left -= 3, e += 3 * PP) {
                             load(e + 2 * PP, r2);
                             consume(e, r0);
-                            e += PP;
-                            if (e >= n) break;
-                            load(e + 2 * PP, r0);
-                            consume(e, r1);
-                            e += PP;
-                            if (e >= n) break;
-                            load(e + 2 * PP, r1);
-                            consume(e, r2);
-                            e += PP;
+                            load(e + 3 * PP, r0);
+                            consume(e + PP, r1);
+                            load(e + 4 * PP, r1);
+                            consume(e + 2 * PP, r2);
                         }
+                        if (left >= 1) consume(e, r0);
+                        if (left == 2) consume(e + PP, r1);
                     }
                 }
                 cached += n;
