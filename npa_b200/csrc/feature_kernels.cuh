@@ -122,12 +122,23 @@ __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x,
 // periodic grid the image of each pair is recovered from the raw difference (x_j - x_i is within half
 // a box of a multiple of the box length) and applied with the same error-free shifted origin as the
 // cell walk uses.
+// Starts `width` floats at `row` on their way into L1 (one or two lines; rows are read in pieces of at
+// most 128 bytes).
+__device__ inline void prefetch_row(const float *row, int width) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(row));
+    if ((reinterpret_cast<uintptr_t>(row) & 127) != 0 && width > 4) asm volatile("prefetch.global.L1 [%0];" ::"l"(row + width - 1));
+}
+
+// `rows` (optional): feature rows of `pitch` floats of which stage 3 will read `width` floats per neighbour;
+// they are prefetched as soon as the index is known.
 template <int D, bool PER>
 __device__ inline void expand_pairs(const Geom &g, const float *__restrict__ x, const Pos<D> &pi,
-                                    const int32_t *__restrict__ list, int count, float4 *geo) {
+                                    const int32_t *__restrict__ list, int count, float4 *geo,
+                                    const float *__restrict__ rows = nullptr, int pitch = 0, int width = 0) {
     const int lane = threadIdx.x & 31;
     for (int e = lane; e < count; e += 32) {
         const int j = __ldg(list + e);
+        if (rows) prefetch_row(rows + (long long)j * pitch, width);
         const Pos<D> pj = load_pos<D>(x, j);
         float rx, ry, rz;
         listed_displacement<D, PER>(g, pi, pj, rx, ry, rz);
@@ -177,6 +188,8 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             if (fvalid && (MASK & F_GRAD)) load_feat<VW>(a.s + i * C + f0, si);
 
             int cached = 0;  // pairs of this particle already written to the neighbour list cache
+            bool from_list = false;
+            const int chunk_w = C - fbase < LPP * VW ? C - fbase : LPP * VW;  // floats of a row read in this chunk
             auto flush = [&](int n) {
                 __syncwarp();
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
@@ -184,6 +197,9 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     const int j = __float_as_int(ge.w);
                     if (a.pair_cache && !a.pair_cache_valid && fbase == 0 && cached + e < a.pair_stride - 1)
                         a.pair_cache[i * a.pair_stride + 1 + cached + e] = j;
+                    // the neighbour's feature row is wanted in stage 3: start it on its way into L1 (the list path
+                    // has done so already, in expand_pairs)
+                    if (!from_list) prefetch_row(a.s + ((long long)j * C + fbase), chunk_w);
                     const float q = sq_norm_fast<D>(ge.x, ge.y, ge.z);
                     const float mj = a.mass ? __ldg(a.mass + j) : 1.0f;
                     const float vj = mj / __ldg(a.rho + j);
@@ -268,8 +284,9 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
             };
             int listed = -1;
             if (a.pair_cache && a.pair_cache_valid) listed = __ldg(a.pair_cache + i * a.pair_stride);
+            from_list = listed >= 0;
             if (listed >= 0 && listed <= kListPerWarp) {
-                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo);
+                expand_pairs<D, PER>(g, a.x, pi, a.pair_cache + i * a.pair_stride + 1, listed, geo, a.s + fbase, C, chunk_w);
                 flush(listed);
             } else if (listed > kListPerWarp) {
                 // a list longer than the warp's pair slots goes through in pieces (the sums carry over); kept apart
@@ -278,7 +295,7 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
 #pragma unroll 1
                 for (int off = 0; off < listed; off += kListPerWarp) {
                     const int n = listed - off < kListPerWarp ? listed - off : kListPerWarp;
-                    expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo);
+                    expand_pairs<D, PER>(g, a.x, pi, list + off, n, geo, a.s + fbase, C, chunk_w);
                     flush(n);
                 }
             } else {
