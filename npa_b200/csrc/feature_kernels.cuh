@@ -175,6 +175,10 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
     for (int k = part; k < it.count; k += g.split) {
         const long long i = it.first + k;
         const Pos<D> pi = load_pos<D>(a.x, i);
+        if (a.pair_cache && a.pair_cache_valid && k + g.split < it.count && lane * 32 < a.pair_stride && lane < 4) {
+            // the head of the next particle's neighbour list (the first 512 bytes) on its way into L1
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(a.pair_cache + (i + g.split) * a.pair_stride + lane * 32));
+        }
         float mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // F_MOMENT: upper triangle, lane-partial over pairs
         float dgs[3] = {0.f, 0.f, 0.f};                   // F_PACK with rho_grad_out: density gradient, lane-partial over pairs
         for (int fbase = 0; fbase < C; fbase += LPP * VW) {
@@ -473,6 +477,24 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
 
             auto flush = [&](int n) {
                 __syncwarp();
+                auto fetch = [&](int e, int slot) {
+                    if (e < n) {
+                        const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
+                        Piece<VW> *dst = ring + slot * NP * 32;
+                        if (FULL) async_copy<VW * 4>(dst, a.s + row);
+                        if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + row);
+                        if (MASK & F_GRAD) {
+#pragma unroll
+                            for (int d = 0; d < D; ++d)
+                                async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (row * D + d * VW));
+                        }
+                    }
+                    async_commit();
+                };
+                if (kBwdRing && FULL && fvalid) {  // the rows of the first S pairs travel while stage 2 computes
+#pragma unroll
+                    for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
+                }
                 for (int e = lane; e < n; e += 32) {  // stage 2: pair scalars, one entry per lane
                     const float4 ge = geo[e];
                     const int j = __float_as_int(ge.w);
@@ -576,22 +598,6 @@ feature_backward_kernel(FeatureBwdArgs a, Geom g) {
                             e += PP;
                         }
                     } else {
-                        auto fetch = [&](int e, int slot) {
-                            if (e < n) {
-                                const long long row = (long long)__float_as_int(geo[e].w) * C + f0;
-                                Piece<VW> *dst = ring + slot * NP * 32;
-                                if (FULL) async_copy<VW * 4>(dst, a.s + row);
-                                if (MASK & F_BLUR) async_copy<VW * 4>(dst + 32, a.g_blur + row);
-                                if (MASK & F_GRAD) {
-#pragma unroll
-                                    for (int d = 0; d < D; ++d)
-                                        async_copy<VW * 4>(dst + (2 + d) * 32, a.g_grad + (row * D + d * VW));
-                                }
-                            }
-                            async_commit();
-                        };
-#pragma unroll
-                        for (int p = 0; p < S; ++p) fetch(sg + p * PP, p);
                         int slot = 0;
                         for (int e = sg; e < n; e += PP) {
                             async_wait<S - 1>();
