@@ -29,7 +29,7 @@ struct HiddenGradArgs {
     int out_dim, out4;  // out4 = out_dim rounded up to a multiple of 4
 };
 
-__global__ void __launch_bounds__(kHgThreads) mlp_hidden_grad_kernel(HiddenGradArgs a) {
+__global__ void __launch_bounds__(kHgThreads, 3) mlp_hidden_grad_kernel(HiddenGradArgs a) {
     __shared__ __align__(16) float w2s[kHgMaxOut][kHgHidden];
     __shared__ __align__(16) float dys[kHgWarps][kHgRows][kHgMaxOut];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,9 +106,9 @@ int npa_mlp_hidden_grad(const float *dy, const float *W2, const float *h, float 
     HiddenGradArgs a = {dy, W2, h, dh, rows, w_stride_out, w_stride_in, out_dim, (out_dim + 3) / 4 * 4};
     const long long groups = (rows + kHgRows - 1) / kHgRows;
     const long long want = (groups + kHgWarps - 1) / kHgWarps;
-    // three CTAs fit per SM (84 registers x 256 threads); a fourth per SM in the queue evens out the tail
-    // (measured: 4 x 148 is faster than 3 x 148 at 131,072 and 262,144 rows)
-    const int ctas = (int)(want < 148 * 4 ? want : 148 * 4);
+    // three CTAs per SM, all resident (the launch bounds cap the kernel at 80 registers; at 84 only two fit
+    // and a grid of 3 or 4 x 148 ran as two waves)
+    const int ctas = (int)(want < 148 * 3 ? want : 148 * 3);
     mlp_hidden_grad_kernel<<<ctas, kHgThreads, 0, (cudaStream_t)stream>>>(a);
     return check_launch("mlp_hidden_grad_kernel");
 }
