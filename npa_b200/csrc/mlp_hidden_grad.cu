@@ -45,6 +45,11 @@ __global__ void __launch_bounds__(kHgThreads, 3) mlp_hidden_grad_kernel(HiddenGr
         const long long r0 = g * kHgRows;
         // the eight rows of dy are contiguous: r0 * O .. (r0 + 8) * O
         const long long first = r0 * O, limit = a.rows * O;
+        {   // the next pass's rows of dy (at most 12 lines) and this pass's rows of h (32 lines) towards L1
+            const long long nfirst = first + (long long)gridDim.x * kHgWarps * kHgRows * O;
+            if (lane * 32 < kHgRows * O && nfirst + lane * 32 < limit) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.dy + nfirst + lane * 32));
+            if (r0 + (lane >> 2) < a.rows) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.h + r0 * kHgHidden + lane * 32));
+        }
         for (int e = lane; e < kHgRows * O4; e += 32) {
             const int r = e / O4, o = e - r * O4;
             const long long at = first + (long long)r * O + o;
