@@ -122,6 +122,27 @@ __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x,
 // periodic grid the image of each pair is recovered from the raw difference (x_j - x_i is within half
 // a box of a multiple of the box length) and applied with the same error-free shifted origin as the
 // cell walk uses.
+// Two fp32 lanes in one 64-bit register pair and the packed arithmetic of sm_100 on them: one issue slot per
+// two multiply-adds, each lane rounded exactly like the scalar instruction.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // Starts `width` floats at `row` on their way into L1 (one or two lines; rows are read in pieces of at
 // most 128 bytes).
 __device__ inline void prefetch_row(const float *row, int width) {
@@ -190,6 +211,12 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
 #pragma unroll
             for (int q = 0; q < VW * D; ++q) gr[q] = 0.f;
             if (fvalid && (MASK & F_GRAD)) load_feat<VW>(a.s + i * C + f0, si);
+            // VW == 4: the sums live in packed pairs while the pairs are drained -- blur of features (0, 1) and (2, 3),
+            // then per axis the gradient of (0, 1) and (2, 3) -- and are unpacked into blur[] / gr[] afterwards
+            unsigned long long pacc[2 + 2 * D];
+#pragma unroll
+            for (int q = 0; q < 2 + 2 * D; ++q) pacc[q] = 0ull;
+            const unsigned long long nsi01 = pack2(-si[0], -si[VW == 4 ? 1 : 0]), nsi23 = pack2(-si[VW == 4 ? 2 : 0], -si[VW == 4 ? 3 : 0]);
 
             int cached = 0;  // pairs of this particle already written to the neighbour list cache
             bool from_list = false;
@@ -245,14 +272,33 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     // through three rotating register sets, the rows of the next two pairs in flight
                     auto consume = [&](int e, const float (&sj)[VW]) {
                         const float4 en = ent[e];
-#pragma unroll
-                        for (int q = 0; q < VW; ++q) {
-                            if (MASK & F_BLUR) blur[q] = fmaf(en.w, sj[q], blur[q]);
+                        if (VW == 4) {
+                            const unsigned long long s01 = pack2(sj[0], sj[VW == 4 ? 1 : 0]), s23 = pack2(sj[VW == 4 ? 2 : 0], sj[VW == 4 ? 3 : 0]);
+                            if (MASK & F_BLUR) {
+                                const unsigned long long ww = pack2(en.w, en.w);
+                                pacc[0] = fma2(ww, s01, pacc[0]);
+                                pacc[1] = fma2(ww, s23, pacc[1]);
+                            }
                             if (MASK & F_GRAD) {
-                                const float df = sj[q] - si[q];
-                                gr[q * D + 0] = fmaf(df, en.x, gr[q * D + 0]);
-                                gr[q * D + 1] = fmaf(df, en.y, gr[q * D + 1]);
-                                if (D == 3) gr[q * D + 2] = fmaf(df, en.z, gr[q * D + 2]);
+                                const unsigned long long d01 = add2(s01, nsi01), d23 = add2(s23, nsi23);  // s_j - s_i
+                                const float kd[3] = {en.x, en.y, en.z};
+#pragma unroll
+                                for (int d = 0; d < D; ++d) {
+                                    const unsigned long long kk = pack2(kd[d], kd[d]);
+                                    pacc[2 + 2 * d] = fma2(d01, kk, pacc[2 + 2 * d]);
+                                    pacc[3 + 2 * d] = fma2(d23, kk, pacc[3 + 2 * d]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < VW; ++q) {
+                                if (MASK & F_BLUR) blur[q] = fmaf(en.w, sj[q], blur[q]);
+                                if (MASK & F_GRAD) {
+                                    const float df = sj[q] - si[q];
+                                    gr[q * D + 0] = fmaf(df, en.x, gr[q * D + 0]);
+                                    gr[q * D + 1] = fmaf(df, en.y, gr[q * D + 1]);
+                                    if (D == 3) gr[q * D + 2] = fmaf(df, en.z, gr[q * D + 2]);
+                                }
                             }
                         }
                     };
@@ -308,6 +354,15 @@ feature_forward_kernel(FeatureFwdArgs a, Geom g) {
                     a.pair_cache[i * a.pair_stride] = cached <= a.pair_stride - 1 ? cached : -1;
             }
 
+            if (VW == 4) {
+                unpack2(pacc[0], blur[0], blur[VW == 4 ? 1 : 0]);
+                unpack2(pacc[1], blur[VW == 4 ? 2 : 0], blur[VW == 4 ? 3 : 0]);
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    unpack2(pacc[2 + 2 * d], gr[0 * D + d], gr[(VW == 4 ? 1 : 0) * D + d]);
+                    unpack2(pacc[3 + 2 * d], gr[(VW == 4 ? 2 : 0) * D + d], gr[(VW == 4 ? 3 : 0) * D + d]);
+                }
+            }
             if (MASK & F_BLUR) {
 #pragma unroll
                 for (int q = 0; q < VW; ++q) blur[q] = g.c_s * across_subgroups<LPP>(blur[q]);
