@@ -157,6 +157,32 @@ __device__ inline float sq_norm_fast(float rx, float ry, float rz) {
     return q;
 }
 
+// Two fp32 lanes in one 64-bit register pair and the packed arithmetic of sm_100 on them: one issue slot per
+// two multiply-adds, each lane rounded exactly like the scalar instruction.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // Spiky pair factors for 0 < q < h2: phi = 3 (h - d)^2 / d with
 // d = sqrt(q + 1e-12), so that K(r) = phi * r; psi = 3 (h^2 - d^2) / d^3 so that
 // dK/dr = phi * I - psi * r r^T.

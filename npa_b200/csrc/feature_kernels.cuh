@@ -122,27 +122,6 @@ __device__ inline void collect_pairs(const Geom &g, const float *__restrict__ x,
 // periodic grid the image of each pair is recovered from the raw difference (x_j - x_i is within half
 // a box of a multiple of the box length) and applied with the same error-free shifted origin as the
 // cell walk uses.
-// Two fp32 lanes in one 64-bit register pair and the packed arithmetic of sm_100 on them: one issue slot per
-// two multiply-adds, each lane rounded exactly like the scalar instruction.
-__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-
 // Starts `width` floats at `row` on their way into L1 (one or two lines; rows are read in pieces of at
 // most 128 bytes).
 __device__ inline void prefetch_row(const float *row, int width) {

@@ -178,6 +178,9 @@ scalar_forward_shared_kernel(ScalarFwdArgs a, Geom g, int span, int batch) {
     // the neighbour count must agree bit for bit with the fp32 oracle on borderline pairs (r^2 without
     // fused multiply-adds); every other output is continuous at the cut-off
     constexpr bool kExact = (MASK & S_COUNT) != 0;
+    // density alone on a clamped grid: two candidates per step in packed fp32x2 arithmetic (the staged
+    // candidates are kept as four arrays x[32] y[32] z[32] m[32], so that a pair is one 8-byte broadcast)
+    constexpr bool kPacked = !PER && MASK == S_DENSITY;
     const int K = a.pair_stride;
 
     bool finished = false;
@@ -223,6 +226,7 @@ scalar_forward_shared_kernel(ScalarFwdArgs a, Geom g, int span, int batch) {
                 const Pos<D> pi = load_pos<D>(a.x, i);
                 int32_t *list = a.pair_cache ? a.pair_cache + i * K + 1 : nullptr;
                 float cnt = 0.f, rho = 0.f, dg[3] = {0.f, 0.f, 0.f}, mom[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                unsigned long long rho2 = 0ull;  // kPacked: sums over the even and the odd candidates of the batches
                 int listed = 0;
 
                 // candidates are staged 32 at a time; the next batch is fetched from global memory while the
@@ -248,7 +252,12 @@ scalar_forward_shared_kernel(ScalarFwdArgs a, Geom g, int span, int batch) {
                     const int4 rg = rng[r];
                     float4 *cand = s_cand[warp][buf];
                     float *cvol = s_vol[warp][buf];
-                    cand[lane] = c_next;
+                    if (kPacked) {
+                        float *cs = reinterpret_cast<float *>(cand);
+                        cs[lane] = c_next.x; cs[32 + lane] = c_next.y; cs[64 + lane] = c_next.z; cs[96 + lane] = c_next.w;
+                    } else {
+                        cand[lane] = c_next;
+                    }
                     if (MASK & S_MOMENT) cvol[lane] = v_next;
                     __syncwarp();
                     // the batch after this one
@@ -258,7 +267,32 @@ scalar_forward_shared_kernel(ScalarFwdArgs a, Geom g, int span, int batch) {
                         jn0 = rn < nr ? rng[rn].x : 0;
                     }
                     fetch(rn, jn0, c_next, v_next);
-                    if (ivalid) {
+                    if (kPacked && ivalid) {
+                        const unsigned long long *cs = reinterpret_cast<const unsigned long long *>(cand);
+                        const unsigned long long nox = pack2(-pi.x, -pi.x), noy = pack2(-pi.y, -pi.y), noz = pack2(-pi.z, -pi.z);
+                        const int jn = min(32, rg.y - j0);
+#pragma unroll 2
+                        for (int k = 0; k < jn; k += 2) {
+                            // candidates k and k + 1 (a batch that ends on an odd count is followed by a zero-mass entry)
+                            const unsigned long long rx = add2(cs[k >> 1], nox), ry = add2(cs[16 + (k >> 1)], noy);
+                            unsigned long long q = fma2(ry, ry, mul2(rx, rx));
+                            if (D == 3) {
+                                const unsigned long long rz = add2(cs[32 + (k >> 1)], noz);
+                                q = fma2(rz, rz, q);
+                            }
+                            float q0, q1;
+                            unpack2(q, q0, q1);
+                            const bool acc0 = q0 < g.h2, acc1 = q1 < g.h2 && k + 1 < jn;
+                            if (list) {
+                                if (acc0 && listed < K - 1) list[listed] = j0 + k;
+                                listed += acc0 ? 1 : 0;
+                                if (acc1 && listed < K - 1) list[listed] = j0 + k + 1;
+                                listed += acc1 ? 1 : 0;
+                            }
+                            const unsigned long long t = pack2(fmaxf(g.h2 - q0, 0.f), fmaxf(g.h2 - q1, 0.f));
+                            rho2 = fma2(cs[48 + (k >> 1)], mul2(mul2(t, t), t), rho2);
+                        }
+                    } else if (ivalid) {
                         const Origin<D, PER> org = make_origin<D, PER>(g, pi.x, pi.y, pi.z, rg.z);
                         const int jn = min(32, rg.y - j0);
 #pragma unroll 4
@@ -307,6 +341,11 @@ scalar_forward_shared_kernel(ScalarFwdArgs a, Geom g, int span, int batch) {
                     buf ^= 1;
                 }
                 __syncwarp();
+                if (kPacked) {
+                    float lo, hi;
+                    unpack2(rho2, lo, hi);
+                    rho = lo + hi;
+                }
                 if (ivalid) {
                     if (list) list[-1] = listed <= K - 1 ? listed : -1;
                     if ((MASK & S_COUNT) && a.count) a.count[i] = cnt;
